@@ -54,13 +54,18 @@ class CacheNeed:
     """What a mixer asks of the cache for one entry. `v_dim` is the width of a value where it
     differs from a key's (0: the same); `keep_first` first tokens of a sequence stay in sight of
     every later query although a window is set; `layout` fixes the tile layout (None: by type
-    and head size)."""
+    and head size). `chunk` > 0: a query sees only the keys of its own run of `chunk` positions
+    counted from the sequence's start, so pages before the run of the next query are given back.
+    `values_in_keys`: a key's value is part of the key's own row (a latent cache); the group then
+    keeps no value storage, and an entry's values are its keys."""
     n_kv: int
     head_dim: int
     window: int = 0   # 0: all keys
     v_dim: int = 0
     keep_first: int = 0
     layout: Optional[int] = None
+    chunk: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -85,19 +90,20 @@ class CacheGroup:
         self.v_layout = tile_layout(dtype, need.value_dim) if need.layout is None else need.layout
         if device is not None:
             self.k = _aligned_zeros(shape, dtype, device)
-            self.v = _aligned_zeros(vshape, dtype, device)
+            self.v = self.k if need.values_in_keys else _aligned_zeros(vshape, dtype, device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = None
         self.table = np.zeros((max_slots, max_pages_per_seq), dtype=np.int32)
         # pages held by a slot: [0, kept) and [first_page, end_page), where kept covers the
         # first tokens a window keeps in sight (none without such tokens) and never gives back
-        self.keep_pages = pages_for(need.keep_first) if need.window > 0 else 0
+        self.keep_pages = pages_for(need.keep_first) if (need.window > 0 or need.chunk > 0) else 0
         self.first_page = np.zeros((max_slots,), dtype=np.int64)   # first page of the window's run
         self.end_page = np.zeros((max_slots,), dtype=np.int64)     # one past the last page held
         self.n_held = np.zeros((max_slots,), dtype=np.int64)       # pages held in all
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return len(self.entries) * self.need.n_kv * (self.need.head_dim + self.need.value_dim) * itemsize
+        per_head = self.need.head_dim + (0 if self.need.values_in_keys else self.need.value_dim)
+        return len(self.entries) * self.need.n_kv * per_head * itemsize
 
     def reserve(self, slot: int, new_len: int) -> None:
         want_end = pages_for(new_len)
@@ -115,12 +121,15 @@ class CacheGroup:
             self.end_page[slot] = want_end
 
     def trim(self, slot: int, length: int) -> None:
-        """After a step: a group with a window gives back the pages that no later
-        query can see (the next query sits at position `length`)."""
-        w = self.need.window
-        if w <= 0:
+        """After a step: a group with a window or with chunks gives back the pages that no
+        later query can see (the next query sits at position `length`)."""
+        w, c = self.need.window, self.need.chunk
+        if w <= 0 and c <= 0:
             return
-        first_needed = min(max(0, length - w + 1) // PAGE, int(self.end_page[slot]))
+        first_pos = max(0, length - w + 1) if w > 0 else 0
+        if c > 0:
+            first_pos = max(first_pos, length // c * c)
+        first_needed = min(first_pos // PAGE, int(self.end_page[slot]))
         first = max(int(self.first_page[slot]), self.keep_pages)    # pages of kept tokens stay
         if first_needed > first:
             n = first_needed - first

@@ -4,8 +4,9 @@ from .registry import (config_class_for, config_from_dict, known_architectures, 
 from .qwen3 import Qwen3Config
 from .dabevik import DabevikConfig
 from .rasezen import RasezenConfig
+from .lebelix import LebelixConfig
 from .params import ParametersFile, SamplingDefaults
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig", "RasezenConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig", "RasezenConfig", "LebelixConfig",
            "config_class_for", "config_from_dict", "known_architectures", "load_config",
            "register_architecture", "ParametersFile", "SamplingDefaults"]

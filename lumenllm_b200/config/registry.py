@@ -85,6 +85,14 @@ def load_config(folder):
     if not path.exists():
         raise ConfigError(f"missing file: {path}")
     config = config_from_dict(_read_json(path))
+    if hasattr(config, "sized_by"):
+        # sizes that config.json leaves to the tensors' shapes
+        from ..weights.loader import WeightError, open_checkpoint
+        try:
+            infos = open_checkpoint(folder)
+        except WeightError:
+            infos = {}          # no checkpoint here: whoever needs the sizes says so
+        config = config.sized_by(lambda name: tuple(infos[name].shape) if name in infos else None)
     gen = folder / "generation_config.json"
     if gen.exists():
         more = eos_ids_of(_read_json(gen).get("eos_token_id"), gen.name)

@@ -33,6 +33,8 @@ MODULES = {
     "layer_ops": (["layer_ops.cu"], ["common.cuh"]),
     "attn_talk": (["attn_talk.cu"], ["common.cuh", "mma_utils.cuh"]),
     "ssm": (["ssm.cu"], ["common.cuh"]),
+    "head_ops": (["head_ops.cu"], ["common.cuh"]),
+    "delta_rule": (["delta_rule.cu"], ["common.cuh"]),
     "moe": (["moe.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "qk_head.cuh", "attn_decode_noalloc.h"]),

@@ -658,9 +658,9 @@ def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale
     require(block_table, I32, "attn.block_table")
     require(tok_seq, I32, "attn.tok_seq")
     require(tok_pos, I32, "attn.tok_pos")
-    if d > 256 or dv > 256 or kcache.shape[3] != d or tuple(vcache.shape[1:3]) != tuple(kcache.shape[1:3]):
-        raise KernelError(f"attention takes key and value sizes up to 256 and caches that fit them, not {d} / {dv} "
-                          f"with {tuple(kcache.shape)} / {tuple(vcache.shape)}")
+    if d > 1024 or dv > 512 or kcache.shape[3] != d or tuple(vcache.shape[1:3]) != tuple(kcache.shape[1:3]):
+        raise KernelError(f"attention takes key sizes up to 1024, value sizes up to 512 and caches that fit them, not "
+                          f"{d} / {dv} with {tuple(kcache.shape)} / {tuple(vcache.shape)}")
     out = torch.empty((N, nq, dv), dtype=q.dtype, device=q.device)
     f = fn("attn_generic", "lumen_attn_generic",
            [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P])
@@ -668,6 +668,253 @@ def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale
             ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, dv, int(window), float(scale), int(layout),
             int(v_layout), stream_ptr()), "attn_generic")
     return out
+
+
+def attn_generic_opt(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale, layout=LAYOUT_LINEAR,
+                     v_layout=None, chunk=0, softcap=0.0, sink=False, values_in_keys=False, value_dim=None,
+                     gate=None, gate_col=0):
+    """attn_generic with options. `chunk` > 0: a query sees only keys of its own run of `chunk`
+    positions (counted from the sequence's start); `softcap` > 0: scores become softcap *
+    tanh(score / softcap); `sink`: the softmax's denominator has one more term exp(0);
+    `values_in_keys`: a key's value is the first `value_dim` numbers of the key's row (vcache is
+    not read); `gate` (float32 [N, W] or [S, N, W] partial sums): the output is multiplied by
+    sigmoid of its columns gate_col + head * dv + e. q may be float32 over a bfloat16 cache; the
+    output has q's type."""
+    N, nq, d = q.shape
+    nkv = kcache.shape[1]
+    dv = int(value_dim) if values_in_keys else vcache.shape[3]
+    v_layout = layout if (v_layout is None or values_in_keys) else v_layout
+    require(q, q.dtype, "attn.q")
+    require(kcache, kcache.dtype, "attn.kcache")
+    if not values_in_keys:
+        require(vcache, kcache.dtype, "attn.vcache")
+    if q.dtype not in (F32, kcache.dtype):
+        raise KernelError(f"attention: queries are float32 or of the cache's type, not {q.dtype} over {kcache.dtype}")
+    for t, nm in ((block_table, "block_table"), (tok_seq, "tok_seq"), (tok_pos, "tok_pos")):
+        require(t, I32, f"attn.{nm}")
+    if d > 1024 or dv > 512 or kcache.shape[3] != d or (values_in_keys and dv > d):
+        raise KernelError(f"attention takes key sizes up to 1024 and value sizes up to 512, not {d} / {dv}")
+    gS = gstride = gW = 0
+    if gate is not None:
+        gate, gS = _partials(gate, "attn.gate")
+        gW, gstride = gate.shape[2], gate.shape[1] * gate.shape[2]
+        if gate.shape[1] != N:
+            raise KernelError("attention: the gate has one row a token")
+    out = torch.empty((N, nq, dv), dtype=q.dtype, device=q.device)
+    f = fn("attn_generic", "lumen_attn_generic_opt",
+           [P, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+            c_int, c_float, c_int, c_int, P, c_int, c_longlong, c_int, c_int, P])
+    check(f(ptr(q), 1 if q.dtype == F32 else 0, ptr(kcache), ptr(kcache if values_in_keys else vcache), ptr(block_table),
+            block_table.stride(0), ptr(tok_seq), ptr(tok_pos), ptr(out), _is_bf16(kcache), N, nq, nkv, d, dv,
+            int(window), float(scale), int(layout), int(v_layout), int(chunk), float(softcap or 0.0), 1 if sink else 0,
+            1 if values_in_keys else 0, ptr(gate), gS, gstride, gW, int(gate_col), stream_ptr()), "attn_generic_opt")
+    return out
+
+
+def qkv_head_norm_store(qkv, bias, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_seq, block_table, kcache,
+                        vcache, nq, nkv, d, dv, out_dtype, k_layout=LAYOUT_LINEAR, v_layout=LAYOUT_LINEAR,
+                        store_kv=True):
+    """Biases, an RMS norm of every query and key head (weights of d values, or None), rotation of
+    the first rotary_dim values of every query and key head by the angles of `cs`, q out as
+    [N, nq, d], keys [pages, nkv, PAGE, d] and values [pages, nkv, PAGE, dv] into the paged cache.
+    qkv float32 [N, W] or [S, N, W] partial sums whose rows begin with nq heads of d, nkv of d and
+    nkv of dv (further columns are not read); bias float32 over those columns or None. With
+    store_kv False only the queries are made."""
+    qkv, S = _partials(qkv, "qkv_head_norm_store.qkv")
+    N, W = qkv.shape[1], qkv.shape[2]
+    used = nq * d + (nkv * (d + dv) if store_kv else 0)
+    if W < used:
+        raise KernelError(f"qkv_head_norm_store: rows of {W} are narrower than the {used} columns of q, k and v")
+    for t, nm, n in ((bias, "bias", used), (q_norm_w, "q_norm", d), (k_norm_w, "k_norm", d)):
+        if t is not None:
+            require(t, F32, f"qkv_head_norm_store.{nm}")
+            if t.numel() < n:
+                raise KernelError(f"qkv_head_norm_store: {nm} must have {n} values")
+    if rotary_dim:
+        require(cs, F32, "qkv_head_norm_store.cs")
+        if tuple(cs.shape) != (N, rotary_dim // 2, 2):
+            raise KernelError(f"qkv_head_norm_store: angles {tuple(cs.shape)} do not fit {N} tokens and {rotary_dim}")
+    for t, nm in ((cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
+        require(t, I32, nm)
+        if t.numel() < N:
+            raise KernelError(f"{nm} shorter than the token count")
+    require(block_table, I32, "block_table")
+    if store_kv:
+        require(kcache, out_dtype, "kcache")
+        require(vcache, out_dtype, "vcache")
+        if tuple(kcache.shape[1:]) != (nkv, PAGE, d) or tuple(vcache.shape[1:]) != (nkv, PAGE, dv):
+            raise KernelError(f"qkv_head_norm_store: caches {tuple(kcache.shape)}, {tuple(vcache.shape)} do not fit "
+                              f"{nkv} kv heads of {d} and {dv}")
+    q_out = torch.empty((N, nq, d), dtype=out_dtype, device=qkv.device)
+    f = fn("head_ops", "lumen_qkv_head_norm_store",
+           [P, c_int, c_longlong, c_int, P, P, P, c_float, P, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
+            c_int, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(qkv), S, N * W, W, ptr(bias), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(cs) if rotary_dim else 0,
+            int(rotary_dim), ptr(cache_pos), ptr(tok_seq), ptr(block_table), block_table.stride(0), ptr(q_out),
+            ptr(kcache) if store_kv else 0, ptr(vcache) if store_kv else 0, _is_bf16(q_out), N, nq, nkv, d, dv,
+            int(k_layout), int(v_layout), 1 if store_kv else 0, stream_ptr()), "qkv_head_norm_store")
+    return q_out
+
+
+def latent_store(u, col, rank, rot_width, norm_w, eps, cs, rotary_dim, cache_pos, tok_seq, block_table, cache):
+    """What latent attention keeps of a token: columns col .. col + rank of the projection u (float32
+    [N, W] or partial sums), RMS-normed with norm_w, and behind them the next rot_width columns with
+    their first rotary_dim values rotated by `cs`; written as one row [rank + rot_width] of the paged
+    cache [pages, 1, PAGE, rank + rot_width] (plain tiles)."""
+    u, S = _partials(u, "latent_store.u")
+    N, W = u.shape[1], u.shape[2]
+    require(norm_w, F32, "latent_store.norm_w")
+    if norm_w.numel() != rank or tuple(cache.shape[1:]) != (1, PAGE, rank + rot_width):
+        raise KernelError(f"latent_store: weight of {norm_w.numel()}, cache {tuple(cache.shape)} do not fit a latent "
+                          f"of {rank} + {rot_width}")
+    if rotary_dim:
+        require(cs, F32, "latent_store.cs")
+        if tuple(cs.shape) != (N, rotary_dim // 2, 2):
+            raise KernelError(f"latent_store: angles {tuple(cs.shape)} do not fit {N} tokens and {rotary_dim}")
+    for t, nm in ((cache_pos, "cache_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        require(t, I32, f"latent_store.{nm}")
+    f = fn("head_ops", "lumen_latent_store",
+           [P, c_int, c_longlong, c_int, c_int, c_int, c_int, P, c_float, P, c_int, P, P, P, c_int, P, c_int, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(col), int(rank), int(rot_width), ptr(norm_w), float(eps),
+            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(cache_pos), ptr(tok_seq), ptr(block_table),
+            block_table.stride(0), ptr(cache), _is_bf16(cache), N, stream_ptr()), "latent_store")
+
+
+def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim):
+    """Queries carried into the latent space: q float32 [N, W] or partial sums, rows of `heads` heads
+    of [d | rot_width]; up_k [heads * d, rank] (the keys' up-projection). Returns float32 [N, heads,
+    rank + rot_width]: sum_j q[h, j] up_k[h d + j, :], then the rot_width values with the first
+    rotary_dim rotated by `cs`."""
+    q, S = _partials(q, "latent_query.q")
+    N, W = q.shape[1], q.shape[2]
+    if tuple(up_k.shape) != (heads * d, rank) or not up_k.is_contiguous() or W < heads * (d + rot_width):
+        raise KernelError(f"latent_query: up-projection {tuple(up_k.shape)} and rows of {W} do not fit {heads} heads "
+                          f"of {d} + {rot_width} over a latent of {rank}")
+    if rotary_dim:
+        require(cs, F32, "latent_query.cs")
+        if tuple(cs.shape) != (N, rotary_dim // 2, 2):
+            raise KernelError(f"latent_query: angles {tuple(cs.shape)} do not fit {N} tokens and {rotary_dim}")
+    out = torch.empty((N, heads, rank + rot_width), dtype=F32, device=q.device)
+    f = fn("head_ops", "lumen_latent_query",
+           [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, P])
+    check(f(ptr(q), S, N * W, W, ptr(up_k), _is_bf16(up_k), int(heads), int(d), int(rot_width), int(rank),
+            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(out), N, stream_ptr()), "latent_query")
+    return out
+
+
+def head_product(x, w, out_dtype):
+    """out[n, h, :] = w_h x[n, h, :] with w [heads * E, J] cut into `heads` matrices [E, J]; x float32
+    [N, heads, J]; returns [N, heads * E] in out_dtype."""
+    require(x, F32, "head_product.x")
+    N, H, J = x.shape
+    if w.dim() != 2 or w.shape[1] != J or w.shape[0] % H or not w.is_contiguous():
+        raise KernelError(f"head_product: weight {tuple(w.shape)} does not fit {H} heads of {J}")
+    E = w.shape[0] // H
+    out = torch.empty((N, H * E), dtype=out_dtype, device=x.device)
+    f = fn("head_ops", "lumen_head_product", [P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(x), ptr(w), _is_bf16(w), ptr(out), _is_bf16(out), N, H, J, E, stream_ptr()), "head_product")
+    return out
+
+
+def gelu_tanh(z, out_dtype):
+    """0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); z float32 [N, F] or [S, N, F] partial sums."""
+    z, S = _partials(z, "gelu_tanh.z")
+    _, N, Fw = z.shape
+    out = torch.empty((N, Fw), dtype=out_dtype, device=z.device)
+    f = fn("head_ops", "lumen_gelu_tanh", [P, c_int, c_longlong, P, c_int, c_longlong, P])
+    check(f(ptr(z), S, N * Fw, ptr(out), _is_bf16(out), N * Fw, stream_ptr()), "gelu_tanh")
+    return out
+
+
+def token_gate(z, tokens, table, col, out_dtype):
+    """gelu_tanh(z[n, c]) * table[tokens[n], col + c]; z float32 [N, C] or partial sums; table [V, W]."""
+    z, S = _partials(z, "token_gate.z")
+    _, N, C = z.shape
+    require(tokens, I32, "token_gate.tokens")
+    if table.dim() != 2 or not table.is_contiguous() or not table.is_cuda or tokens.numel() < N:
+        raise KernelError("token_gate: the table must be a contiguous CUDA matrix, one token a row of z")
+    out = torch.empty((N, C), dtype=out_dtype, device=z.device)
+    f = fn("head_ops", "lumen_token_gate", [P, c_int, c_longlong, P, P, c_int, c_int, c_int, c_int, P, c_int, c_int, P])
+    check(f(ptr(z), S, N * C, ptr(tokens), ptr(table), _is_bf16(table), table.shape[1], int(col), C, ptr(out),
+            _is_bf16(out), N, stream_ptr()), "token_gate")
+    return out
+
+
+def add_cast(h, delta, out_dtype):
+    """h += the partial sums of delta (float32 [N, H] or [S, N, H]; None: nothing to add), in place;
+    returns h in out_dtype."""
+    require(h, F32, "add_cast.h")
+    S = 0
+    if delta is not None:
+        delta, S = _partials(delta, "add_cast.delta")
+        if tuple(delta.shape[1:]) != tuple(h.shape):
+            raise KernelError(f"add_cast: update {tuple(delta.shape)} does not fit the stream {tuple(h.shape)}")
+    out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    f = fn("head_ops", "lumen_add_cast", [P, P, c_int, c_longlong, P, c_int, c_longlong, P])
+    check(f(ptr(h), ptr(delta), S, h.numel(), ptr(out), _is_bf16(out), h.numel(), stream_ptr()), "add_cast")
+    return out
+
+
+def cols_cast(u, col, width, out_dtype):
+    """Columns col .. col + width of u (float32 [N, W] or partial sums, added) in out_dtype."""
+    u, S = _partials(u, "cols_cast.u")
+    _, N, W = u.shape
+    out = torch.empty((N, width), dtype=out_dtype, device=u.device)
+    f = fn("head_ops", "lumen_cols_cast", [P, c_int, c_longlong, c_int, c_int, c_int, P, c_int, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(col), int(width), ptr(out), _is_bf16(out), N, stream_ptr()), "cols_cast")
+    return out
+
+
+def head_norm_gate(y, weight, eps, gate, gate_col, heads, out_dtype):
+    """Every head of y (float32 [N, heads * E]) divided by its root mean square, times weight [E],
+    times sigmoid of the gate's columns gate_col + h E + e (float32 [N, W] or partial sums)."""
+    require(y, F32, "head_norm_gate.y")
+    require(weight, F32, "head_norm_gate.weight")
+    gate, S = _partials(gate, "head_norm_gate.gate")
+    N = y.shape[0]
+    E = y.shape[1] // heads
+    if weight.numel() != E or gate.shape[1] != N or heads * E != y.shape[1]:
+        raise KernelError(f"head_norm_gate: weight of {weight.numel()}, gate {tuple(gate.shape)} do not fit {heads} "
+                          f"heads of {E}")
+    out = torch.empty((N, heads * E), dtype=out_dtype, device=y.device)
+    f = fn("head_ops", "lumen_head_norm_gate",
+           [P, P, c_float, P, c_int, c_longlong, c_int, c_int, P, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(y), ptr(weight), float(eps), ptr(gate), S, N * gate.shape[2], gate.shape[2], int(gate_col), ptr(out),
+            _is_bf16(out), N, int(heads), E, stream_ptr()), "head_norm_gate")
+    return out
+
+
+def delta_rule(x, q_col, k_col, v_col, u, beta_col, a, dt_bias, a_log, state, cu_q, seq_slot, n_seqs, heads, kv_heads,
+               d, dv):
+    """The gated delta rule with a decay a key channel (csrc/delta_rule.cu). x float32 [N, C]: q
+    (kv_heads heads of d from q_col), k (k_col), v (heads of dv from v_col), convolved and activated;
+    u: projection partial sums with the heads' beta logits from beta_col; a: partial sums [.., N,
+    heads * d] of the decay logits; state float32 [slots, heads, dv, d] (row seq_slot[b] sequence
+    b's, updated in place). Returns float32 [N, heads * dv]."""
+    require(x, F32, "delta_rule.x")
+    u, uS = _partials(u, "delta_rule.u")
+    a, aS = _partials(a, "delta_rule.a")
+    N, C = x.shape
+    if u.shape[1] != N or tuple(a.shape[1:]) != (N, heads * d):
+        raise KernelError(f"delta_rule: projections {tuple(u.shape)}, {tuple(a.shape)} do not fit {N} tokens and "
+                          f"{heads} heads of {d}")
+    for t, nm, n in ((dt_bias, "dt_bias", heads * d), (a_log, "a_log", heads)):
+        require(t, F32, f"delta_rule.{nm}")
+        if t.numel() != n:
+            raise KernelError(f"delta_rule: {nm} must have {n} values")
+    require(state, F32, "delta_rule.state", contiguous=False)
+    if tuple(state.shape[1:]) != (heads, dv, d) or not state[0].is_contiguous():
+        raise KernelError(f"delta_rule: state must be float32 [slots, {heads}, {dv}, {d}]")
+    require(cu_q, I32, "delta_rule.cu_q")
+    require(seq_slot, I32, "delta_rule.seq_slot")
+    y = torch.empty((N, heads * dv), dtype=F32, device=x.device)
+    f = fn("delta_rule", "lumen_delta_rule",
+           [P, c_int, c_int, c_int, c_int, P, c_int, c_longlong, c_int, c_int, P, c_int, c_longlong, P, P, P, c_longlong,
+            P, P, c_int, P, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(x), C, int(q_col), int(k_col), int(v_col), ptr(u), uS, N * u.shape[2], u.shape[2], int(beta_col), ptr(a),
+            aS, N * heads * d, ptr(dt_bias), ptr(a_log), ptr(state), state.stride(0), ptr(cu_q), ptr(seq_slot),
+            int(n_seqs), ptr(y), int(heads), int(kv_heads), int(d), int(dv), stream_ptr()), "delta_rule")
+    return y
 
 
 def gemm_f32(a, w, out=None):

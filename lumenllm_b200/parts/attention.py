@@ -1,8 +1,10 @@
 """The attention mixers: grouped-query causal attention over the cache.
 
-"gqa_attention" (GQAttention) norms each head, "wide_norm_attention" (WideNormAttention, at
-the end of this file) norms a whole projection at once, has biases, a value norm and values of
-their own width; both hand their queries to `causal_attention`, which picks the kernel.
+"gqa_attention" (GQAttention) norms each head, "wide_norm_attention" (WideNormAttention)
+norms a whole projection at once, has biases, a value norm and values of their own width,
+"head_norm_attention" (HeadNormAttention, at the end of this file) norms each head, has biases,
+values of their own width, capped scores, chunks, a sink in the softmax and an output gate; all
+hand their queries to `causal_attention`, which picks the kernel.
 
 In order (crates/aegisllm-cuda/src/executor/attention.rs:139-202,241-250,341-352,
 413-425; prompt twin executor/prefill/layer.rs:472-636,810-823,967-1047):
@@ -127,13 +129,19 @@ class GQAttention:
         return causal_attention(q, kc, vc, table, ctx, layout, layout, self.window, self.scale)
 
 
-def causal_attention(q, kc, vc, table, ctx, k_layout, v_layout, window, scale):
+def causal_attention(q, kc, vc, table, ctx, k_layout, v_layout, window, scale, chunk=0, softcap=0.0,
+                     sink=False, gate=None, gate_col=0):
     """Chooses the kernel by the step's shape: the split-KV kernel when every sequence
     brings one token, the flash kernel for prompts, and the general kernel for the
     32-bit path and for head sizes the fast kernels do not take (keys and values of
-    different widths among them). All agree within rounding. q [N, nq, d]."""
+    different widths among them). All agree within rounding. q [N, nq, d].
+    `chunk`, `softcap`, `sink` and `gate` are the options of ops.kernels.attn_generic_opt."""
     nq, d = q.shape[1], q.shape[2]
     nkv, dv = kc.shape[1], vc.shape[3]
+    if chunk or softcap or sink or gate is not None:
+        return K.attn_generic_opt(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, window, scale, layout=k_layout,
+                                  v_layout=v_layout, chunk=chunk, softcap=softcap, sink=sink, gate=gate,
+                                  gate_col=gate_col)
     fast = (k_layout == K.LAYOUT_SW128 and v_layout == K.LAYOUT_SW128 and q.dtype == torch.bfloat16
             and d == dv and d in (64, 128) and nq // nkv <= 16)
     if fast and ctx.is_decode:
@@ -213,4 +221,94 @@ class WideNormAttention:
                                   cs=self.position.angles(ctx) if rot else None, rotary_dim=rot,
                                   value_unit_eps=self.eps if self.value_norm else None)
         out = causal_attention(q, kc, vc, table, ctx, entry.layout, entry.v_layout, self.window, self.scale)
+        return self.o(out.view(-1, self.H * self.dv), split_ok=True, add_to=residual)
+
+
+@register_part("mixer", "head_norm_attention")
+class HeadNormAttention:
+    """q, k, v = y Wq^T (+ bq), y Wk^T (+ bk), y Wv^T (+ bv); every query head and every key head
+    RMS-normed over its `head_dim` values with ONE weight of that size for all heads (plain weight);
+    then the position part's rotation of the first `rotary_dim` values of every query and key head;
+    score = softmax_scale * q . k, and with `softcap` c > 0 then c * tanh(score / c); a query at
+    position p sees key j <= p, with `chunk` n > 0 only where p // n == j // n, with `window` w > 0
+    only where p - j < w; weights exp(s_j) / (sink + sum exp(s_j)) with sink = 1 when `sink` is set
+    (a key of score 0 without a value) and 0 otherwise; query head h reads kv head
+    h // (heads / kv_heads); with `output_gate` the heads' outputs are multiplied by
+    sigmoid(y Wg^T) element by element; o = ctx Wo^T without a bias. Keys are `head_dim` wide,
+    values `value_dim`. Norms, angles, scores and weights are float32. Tensors: `<prefix>.q`, `.k`,
+    `.v` (each with `.b` when `bias`), `.q.norm`, `.k.norm` (when `qk_norm`, the default), `.g`
+    (when `output_gate`), `.o`."""
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(p):
+        return tuple(int(need(p, k, "head_norm_attention")) for k in
+                     ("hidden_size", "num_heads", "num_kv_heads", "head_dim", "value_dim"))
+
+    @classmethod
+    def tensors(cls, spec):
+        p = spec.params
+        D, H, G, d, dv = cls._sizes(p)
+        pre = spec.prefix
+        t = {f"{pre}.q": ((H * d, D), "matrix"), f"{pre}.k": ((G * d, D), "matrix"),
+             f"{pre}.v": ((G * dv, D), "matrix"), f"{pre}.o": ((D, H * dv), "matrix")}
+        if p.get("bias", False):
+            t.update({f"{pre}.q.b": ((H * d,), "matrix"), f"{pre}.k.b": ((G * d,), "matrix"),
+                      f"{pre}.v.b": ((G * dv,), "matrix")})
+        if p.get("qk_norm", True):
+            t.update({f"{pre}.q.norm": ((d,), "norm"), f"{pre}.k.norm": ((d,), "norm")})
+        if p.get("output_gate", False):
+            t[f"{pre}.g"] = ((H * dv, D), "matrix")
+        t.update(part_tensors("position", p["position"]))
+        return t
+
+    def __init__(self, spec, weights, runtime):
+        p = spec.params
+        self.runtime = runtime
+        _, self.H, self.G, self.d, self.dv = self._sizes(p)
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.G} kv heads")
+        if self.d > 512 or self.dv > 512:
+            raise ValueError(f"key size {self.d}, value size {self.dv}: the attention kernels take up to 512")
+        self.window = int(p.get("window", 0) or 0)
+        self.chunk = int(p.get("chunk", 0) or 0)
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.sink = bool(p.get("sink", False))
+        self.scale = float(need(p, "softmax_scale", "head_norm_attention"))
+        self.eps = float(need(p, "norm_eps", "head_norm_attention"))
+        self.position = build_part("position", p["position"], weights, runtime)
+        pre = spec.prefix
+        f32 = lambda n: weights[n].to(device=runtime.device, dtype=torch.float32).contiguous()
+        mats = [weights[f"{pre}.q"], weights[f"{pre}.k"], weights[f"{pre}.v"]]
+        self.gated = bool(p.get("output_gate", False))
+        if self.gated:
+            mats.append(weights[f"{pre}.g"])       # the gate reads the same rows: one product for all four
+        self.proj = Linear.stacked(mats, runtime)
+        self.bias = (torch.cat([f32(f"{pre}.q.b"), f32(f"{pre}.k.b"), f32(f"{pre}.v.b")]).contiguous()
+                     if p.get("bias", False) else None)
+        self.q_norm = self.k_norm = None
+        if p.get("qk_norm", True):
+            self.q_norm, self.k_norm = f32(f"{pre}.q.norm"), f32(f"{pre}.k.norm")
+        self.gate_col = self.H * self.d + self.G * (self.d + self.dv)
+        self.o = Linear(weights[f"{pre}.o"], runtime)
+
+    def cache_need(self):
+        return CacheNeed(self.G, self.d, self.window, v_dim=0 if self.dv == self.d else self.dv, chunk=self.chunk)
+
+    def state_shape(self):
+        return None
+
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, entry, residual=None):
+        kc, vc, table = entry.cache()
+        u = self.proj(y, split_ok=True)            # float32 [q | k | v | gate], possibly partial sums
+        rot = self.position.rotary_dim
+        q = K.qkv_head_norm_store(u, self.bias, self.q_norm, self.k_norm, self.eps,
+                                  self.position.angles(ctx) if rot else None, rot, ctx.cache_pos, ctx.tok_seq, table,
+                                  kc, vc, self.H, self.G, self.d, self.dv, self.runtime.dtype,
+                                  k_layout=entry.layout, v_layout=entry.v_layout)
+        out = causal_attention(q, kc, vc, table, ctx, entry.layout, entry.v_layout, self.window, self.scale,
+                               chunk=self.chunk, softcap=self.softcap, sink=self.sink,
+                               gate=u if self.gated else None, gate_col=self.gate_col)
         return self.o(out.view(-1, self.H * self.dv), split_ok=True, add_to=residual)

@@ -19,6 +19,8 @@ in the constructor and declare their tensors with a classmethod
              offers state_shape() -> (shape, dtype) | None like a mixer (EntryView.state("block"))
   input_conv forward(y, state, ctx, out_dtype) -> what a sublayer reads instead of y
              (y: float32 normed rows; state: the sequences' last inputs, moved on by the call)
+  token_input forward(h, pending, ctx) -> (h, pending): an input from the tokens themselves that a
+             block adds after its sublayers (it may add `pending` into h first)
   head       forward(y) -> logits float32 [W, V]
 
 A delta is a list of S partial sums of one update of the residual stream; the
@@ -38,7 +40,7 @@ import torch
 from ..config.spec import ConfigError, PartSpec
 
 _REGISTRY: Dict[Tuple[str, str], type] = {}
-CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "head", "input_conv")
+CATEGORIES = ("embedding", "norm", "position", "mixer", "ffn", "block", "head", "input_conv", "token_input")
 
 
 def register_part(category: str, kind: str) -> Callable[[type], type]:

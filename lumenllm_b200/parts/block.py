@@ -4,7 +4,9 @@
 (crates/aegisllm-cuda/src/executor/prefill/layer.rs:476-482,1090,1381-1439).
 The adds are not done here: a block hands its last update on as `pending`, and
 the next norm (the next block's, or the model's final one) adds it while it
-reads the stream anyway.
+reads the stream anyway. A layer may lack the feed-forward (and its norm); with
+`extras["token_input"]` a part of that category (parts/token_input.py) runs after the
+sublayers and adds an input that comes from the tokens themselves.
 
 "parallel": h' = h + (mixer(norm(h)) + ffn(norm(h))): ONE norm, whose output both sublayers
 read; a layer may lack the feed-forward. The two updates go on side by side as one stack of
@@ -31,16 +33,27 @@ class PreNormBlock:
         t = {}
         t.update(part_tensors("norm", layer_spec.norms["mixer"]))
         t.update(part_tensors("mixer", layer_spec.mixer))
-        t.update(part_tensors("norm", layer_spec.norms["ffn"]))
-        t.update(part_tensors("ffn", layer_spec.ffn))
+        if layer_spec.ffn is not None:
+            t.update(part_tensors("norm", layer_spec.norms["ffn"]))
+            t.update(part_tensors("ffn", layer_spec.ffn))
+        if "token_input" in layer_spec.extras:
+            t.update(part_tensors("token_input", layer_spec.extras["token_input"]))
         return t
 
     def __init__(self, layer_spec, weights, runtime):
         self.runtime = runtime
         self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], weights, runtime)
         self.mixer = build_part("mixer", layer_spec.mixer, weights, runtime)
-        self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], weights, runtime)
-        self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
+        self.norm_ffn = self.ffn = self.token_input = None
+        if layer_spec.ffn is not None:
+            self.norm_ffn = build_part("norm", layer_spec.norms["ffn"], weights, runtime)
+            self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
+        if "token_input" in layer_spec.extras:
+            self.token_input = build_part("token_input", layer_spec.extras["token_input"], weights, runtime)
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.ffn, self.token_input) if p is not None)
 
     def forward(self, h, pending, ctx, entry):
         # A part that says `adds_residual` is offered the stream itself: it may add its update
@@ -51,11 +64,15 @@ class PreNormBlock:
             a = self.mixer.forward(y, ctx, entry, residual=h)
         else:
             a = self.mixer.forward(y, ctx, entry)
-        y2 = self.norm_ffn.forward(h, a, self.runtime.dtype)
-        if getattr(self.ffn, "adds_residual", False):
-            m = self.ffn.forward(y2, ctx, residual=h)
-        else:
-            m = self.ffn.forward(y2, ctx)
+        m = a
+        if self.ffn is not None:
+            y2 = self.norm_ffn.forward(h, a, self.runtime.dtype)
+            if getattr(self.ffn, "adds_residual", False):
+                m = self.ffn.forward(y2, ctx, residual=h)
+            else:
+                m = self.ffn.forward(y2, ctx)
+        if self.token_input is not None:
+            return self.token_input.forward(h, m, ctx)
         return h, m
 
 

@@ -1,0 +1,100 @@
+"""Latent attention: the keys and values of all heads are products of ONE vector a token.
+
+For H heads with d plain and r rotated query/key values a head, value size dv and latent size R:
+q = y Wq^T, laid out head by head as [d plain | r rotated]; z = y Wdkv^T has R + r values, of which
+the first R, RMS-normed with the weight `.dkv.norm`, are the latent c, and the last r are a key part
+that all heads share; the position part rotates the first `rotary_dim` of the r values of every
+query head and of the shared key part. Head h's plain key is Uk_h c and its value Uv_h c
+(`.uk` [H d, R], `.uv` [H dv, R]); score = softmax_scale * (q_plain . k_plain + q_rot . k_rot);
+a query at position p sees key j if 0 <= p - j < window (window 0: every earlier key); ordinary
+softmax; o = ctx Wo^T.
+
+The cache keeps [c | rotated key part] per token and nothing per head (CacheNeed.values_in_keys:
+one kv head whose rows are R + r wide and whose values are the rows' first R numbers). A query
+head is carried into the latent space, q_plain Uk_h (kernels.latent_query), scores and weighted
+sums are taken over the cached rows by the general attention kernel, and the sums come back through
+Uv_h (kernels.head_product); nothing of a key or value is ever expanded. With `shares_cache` the
+part has no Wdkv and reads the cache of the entry the schedule names, with its own Uk, Uv, queries
+and window; `cache_window` is what the cache must keep in sight (the widest window of its readers).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.kv import LAYOUT_LINEAR, CacheNeed
+from ..ops import kernels as K
+from .base import build_part, need, part_tensors, register_part
+from .linear import Linear
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention:
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(p):
+        return tuple(int(need(p, k, "latent_attention")) for k in
+                     ("hidden_size", "num_heads", "head_dim", "rot_width", "value_dim", "latent_size"))
+
+    @classmethod
+    def tensors(cls, spec):
+        p = spec.params
+        D, H, d, r, dv, R = cls._sizes(p)
+        pre = spec.prefix
+        t = {f"{pre}.q": ((H * (d + r), D), "matrix"), f"{pre}.uk": ((H * d, R), "matrix"),
+             f"{pre}.uv": ((H * dv, R), "matrix"), f"{pre}.o": ((D, H * dv), "matrix")}
+        if not p.get("shares_cache", False):
+            t[f"{pre}.dkv"] = ((R + r, D), "matrix")
+            t[f"{pre}.dkv.norm"] = ((R,), "norm")
+        t.update(part_tensors("position", p["position"]))
+        return t
+
+    def __init__(self, spec, weights, runtime):
+        p = spec.params
+        self.runtime = runtime
+        _, self.H, self.d, self.r, self.dv, self.R = self._sizes(p)
+        if self.R + self.r > 1024 or self.R > 512:
+            raise ValueError(f"a latent of {self.R} + {self.r}: the attention kernel takes rows up to 1024 wide "
+                             "and latents up to 512")
+        self.window = int(p.get("window", 0) or 0)
+        self.cache_window = int(p.get("cache_window", self.window) or 0)
+        self.scale = float(need(p, "softmax_scale", "latent_attention"))
+        self.eps = float(need(p, "norm_eps", "latent_attention"))
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.position = build_part("position", p["position"], weights, runtime)
+        if self.position.rotary_dim > self.r:
+            raise ValueError(f"a rotation over {self.position.rotary_dim} of {self.r} rotated values")
+        pre = spec.prefix
+        mats = [weights[f"{pre}.q"]]
+        self.c_norm = None
+        if not self.shares_cache:
+            mats.append(weights[f"{pre}.dkv"])          # reads the same rows: one product for both
+            self.c_norm = weights[f"{pre}.dkv.norm"].to(device=runtime.device, dtype=torch.float32).contiguous()
+        self.proj = Linear.stacked(mats, runtime)
+        keep = torch.float32 if runtime.is_f32 else None
+        self.uk = weights[f"{pre}.uk"].to(device=runtime.device, dtype=keep).contiguous()
+        self.uv = weights[f"{pre}.uv"].to(device=runtime.device, dtype=keep).contiguous()
+        self.o = Linear(weights[f"{pre}.o"], runtime)
+
+    def cache_need(self):
+        return CacheNeed(1, self.R + self.r, self.cache_window, v_dim=self.R, layout=LAYOUT_LINEAR,
+                         values_in_keys=True)
+
+    def state_shape(self):
+        return None
+
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, entry, residual=None):
+        kc, _, table = entry.cache()
+        u = self.proj(y, split_ok=True)            # float32 [q | c and key part], possibly partial sums
+        rot = self.position.rotary_dim
+        cs = self.position.angles(ctx) if rot else None
+        if entry.writes_cache and not self.shares_cache:
+            K.latent_store(u, self.H * (self.d + self.r), self.R, self.r, self.c_norm, self.eps, cs, rot,
+                           ctx.cache_pos, ctx.tok_seq, table, kc)
+        q = K.latent_query(u, self.uk, self.H, self.d, self.r, self.R, cs, rot)
+        mixed = K.attn_generic_opt(q, kc, None, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
+                                   layout=LAYOUT_LINEAR, values_in_keys=True, value_dim=self.R)
+        out = K.head_product(mixed, self.uv, self.runtime.dtype)
+        return self.o(out, split_ok=True, add_to=residual)

@@ -16,6 +16,9 @@ The activation is one float32 kernel over the product's partial sums.
 "xielu_mlp": u = y Wu^T, out = xIELU(u) Wd^T with xIELU(z) = softplus(p) z^2 + z/2 for z > 0 and
 (1/2 + softplus(q)) (e^z - 1 - z) + z/2 for z <= 0, (p, q) the two values of `<prefix>.act`.
 
+"gelu_mlp": u = y Wu^T, out = gelu_tanh(u) Wd^T with gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi)
+(z + 0.044715 z^3))); tensors `<prefix>.up`, `<prefix>.down`.
+
 "routed_experts": many small SwiGLU experts (`<prefix>.e<i>.gate/up/down`, no biases) of which
 each token uses `top`. The router's logits y Wr^T are float32; s = softmax over ALL router
 outputs; the `top` outputs with the largest s + correction are chosen, and each counts with its
@@ -100,6 +103,28 @@ class PolyNormMLP:
         u = self.up(y, split_ok=True)                       # float32 [N, I], possibly S partials
         z = K.polynorm(u, self.act, self.eps, self.runtime.dtype)
         return self.down(z, split_ok=True)
+
+
+@register_part("ffn", "gelu_mlp")
+class GeluMLP:
+    graph_safe = True
+
+    @classmethod
+    def tensors(cls, spec):
+        H = int(need(spec.params, "hidden_size", "gelu_mlp"))
+        I = int(need(spec.params, "intermediate_size", "gelu_mlp"))
+        return {f"{spec.prefix}.up": ((I, H), "matrix"), f"{spec.prefix}.down": ((H, I), "matrix")}
+
+    def __init__(self, spec, weights, runtime):
+        self.runtime = runtime
+        self.up = Linear(weights[f"{spec.prefix}.up"], runtime)
+        self.down = Linear(weights[f"{spec.prefix}.down"], runtime)
+
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, residual=None):
+        z = K.gelu_tanh(self.up(y, split_ok=True), self.runtime.dtype)      # adds the partial sums, float32
+        return self.down(z, split_ok=True, add_to=residual)
 
 
 @register_part("ffn", "xielu_mlp")
