@@ -241,3 +241,10 @@ def forward(cfg, w, tokens, streams=None):
             streams.append(x.clone())
     y = norm_one_plus(x, w["final.norm"], eps)
     return y @ w["embed"].T
+
+
+def generate_greedy(cfg, w, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
