@@ -107,11 +107,12 @@ def causal_conv_silu(x, taps_w):
 
 # ------------------------------------------------------------------ mixers
 
-def attention(h, w, pre, m, eps):
+def attention(h, w, pre, m, eps, sink=1.0):
     """Biased projections, an RMS norm of every query and key head (one weight of d values for all
     heads), partial rotation, capped scores, sight within the query's own chunk, a softmax whose
     denominator has one more term exp(0) with no value behind it, and a sigmoid gate on the heads'
-    outputs."""
+    outputs. (`sink` 0.0 gives the ordinary softmax; the tests use it to show that a case tells the
+    two apart.)"""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = (h @ w[pre + "q"].T + w[pre + "q.b"]).view(T, H, d)
@@ -133,7 +134,7 @@ def attention(h, w, pre, m, eps):
     s = s.masked_fill(~seen[None], float("-inf"))
     big = torch.clamp(s.max(dim=-1, keepdim=True).values, min=0.0)
     e = torch.exp(s - big)
-    p = e / (torch.exp(-big) + e.sum(dim=-1, keepdim=True))
+    p = e / (sink * torch.exp(-big) + e.sum(dim=-1, keepdim=True))
     o = torch.einsum("hij,jhd->ihd", p, v).reshape(T, H * dv)
     o = o * torch.sigmoid(h @ w[pre + "g"].T)
     return o @ w[pre + "o"].T
@@ -146,7 +147,9 @@ def latent_of(h, w, pre, m, eps):
     T = h.shape[0]
     z = h @ w[pre + "dkv"].T
     c = norm_plain(z[:, :R], w[pre + "dkv.norm"], eps)
-    kr = rotate(z[:, R:].view(T, 1, r), torch.arange(T), m["rot"]["base"], m["rot"]["dims"]).view(T, r)
+    kr = z[:, R:]
+    if m.get("rot"):
+        kr = rotate(kr.reshape(T, 1, r), torch.arange(T), m["rot"]["base"], m["rot"]["dims"]).view(T, r)
     return c, kr
 
 
@@ -158,7 +161,9 @@ def latent_attention(h, w, pre, m, eps, latent):
     c, kr = latent
     q = (h @ w[pre + "q"].T).view(T, H, d + r)
     q_plain = q[..., :d]
-    q_rot = rotate(q[..., d:], torch.arange(T), m["rot"]["base"], m["rot"]["dims"])
+    q_rot = q[..., d:]
+    if m.get("rot"):
+        q_rot = rotate(q_rot, torch.arange(T), m["rot"]["base"], m["rot"]["dims"])
     k_plain = (c @ w[pre + "uk"].T).view(T, H, d)
     v = (c @ w[pre + "uv"].T).view(T, H, dv)
     s = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, kr)) * m["scale"]
