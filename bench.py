@@ -357,7 +357,7 @@ def main() -> int:
                     help="context length (default: the workload's)")
     ap.add_argument("--prompt-len", default=None, metavar="LO:HI",
                     help="prompt lengths are drawn uniformly from this range")
-    ap.add_argument("--design", default=None, choices=["dabevik", "rasezen"],
+    ap.add_argument("--design", default=None, choices=["dabevik", "rasezen", "lebelix"],
                     help="measure this design beside the Qwen3 decoder at equal sizes instead of the benchmark")
     ap.add_argument("--sizes", default="2k,4k", help="with --design: which of compare.SIZES to run")
     args = ap.parse_args()

@@ -14,6 +14,13 @@ kv heads, head size, window and dense feed-forward width; what differs is the de
 blocks with one norm a layer, norms over whole projections, a value norm, some layers whose
 mixer is a state-space recurrence instead of attention, and feed-forwards that are mixtures of
 small experts (their chosen experts and the shared one together about a dense one's size).
+
+Lebelix (`--design lebelix`, LEBELIX_SIZES): the same width, layers, vocabulary, attention heads, kv
+heads, head size, dense feed-forward width, and a window on every layer of the twin as long as
+Lebelix's chunks and windows; what differs is the design: attention with capped scores, chunks, a
+sink and an output gate, layers of latent attention (one of them reading an earlier layer's latent
+cache), layers whose mixer is the gated delta rule, a two-matrix GELU feed-forward, and the
+per-layer token input.
 """
 from __future__ import annotations
 
@@ -36,6 +43,18 @@ RASEZEN_SIZES = {
                ssm=dict(heads=128, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
                moe=dict(ff=1536, experts=16, identity=2, top=4, scale=2.0, shared=3072),
                pattern=["ad", "se", "ae", "se"]),
+}
+# Lebelix: a layer's mixer, "a" attention, "l" latent attention, "L" latent attention that reads the
+# first "l" layer's cache, "c" the gated delta rule; every layer has the dense feed-forward
+LEBELIX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=1024, vocab=32768, rot=64, softcap=50.0,
+               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512),
+               delta=dict(heads=16, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64),
+               side=256, pattern=["l", "a", "a", "c", "L", "a", "c", "a"]),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=2048, vocab=32768, rot=64, softcap=50.0,
+               latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512),
+               delta=dict(heads=32, kv_heads=16, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128),
+               side=256, pattern=["l", "a", "c", "L"]),
 }
 CONTEXT = 4096
 PROMPT_TOKENS = 2048
@@ -63,6 +82,21 @@ def rasezen_config(s):
             "max_positions": CONTEXT, "layers": layers}
 
 
+def lebelix_config(s):
+    attn = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+            "scale": s["dim"] ** -0.5, "mask": {"size": s["window"]}, "softcap": s["softcap"],
+            "rot": {"base": 500000.0, "dims": s["rot"]}}
+    lat = dict(s["latent"], scale=(s["latent"]["dim"] + s["latent"]["rot_dim"]) ** -0.5, mask={"size": s["window"]},
+               rot={"base": 1000000.0, "dims": s["latent"]["rot_dim"]})
+    first = s["pattern"].index("l") if "L" in s["pattern"] else None
+    mixers = {"a": ("attention", attn), "l": ("latent_attention", lat),
+              "L": ("latent_attention", dict(lat, kv_from=first)), "c": ("channel_delta", dict(s["delta"]))}
+    return {"architecture": "Lebelix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": s["width"] ** 0.5}, "token_side": {"dim": s["side"]}, "max_positions": CONTEXT,
+            "layers": [{"type": mixers[p][0], "mixer": mixers[p][1], "mlp": {"kind": "dense", "ff": s["ff"]}}
+                       for p in s["pattern"]]}
+
+
 def qwen3_config(s):
     n_layers = s["layers"] if "layers" in s else len(s["pattern"])
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=s["width"],
@@ -82,10 +116,16 @@ CLASSES = {
     "lumen_attn_prefill": "attention", "lumen_attn_generic": "attention", "lumen_attn_talk": "attention",
     "lumen_attn_talk_prompt": "attention", "lumen_argmax": "sampling", "lumen_sample": "sampling",
     "lumen_gemm_tc_qkv": "qkv product + q/k norm + cache write",
-    "lumen_conv_silu": "state-space: convolution", "lumen_ssm_scan": "state-space: recurrence",
+    "lumen_conv_silu": "recurrence: convolution", "lumen_ssm_scan": "state-space: recurrence",
     "lumen_gated_part_norm": "state-space: gate + norm", "lumen_xielu": "activation",
     "lumen_moe_route": "experts: route + group", "lumen_moe_route_x": "experts: route + group",
     "lumen_moe_group": "experts: route + group",
+    "lumen_qkv_head_norm_store": "q/k norm + cache write", "lumen_attn_generic_opt": "attention (general kernel)",
+    "lumen_attn_prefill_tc_opt": "attention", "lumen_attn_decode_opt": "attention",
+    "lumen_latent_store": "latent: norm + cache write", "lumen_latent_query": "latent: queries into the latent space",
+    "lumen_head_product": "latent: values out of the latent space", "lumen_gelu_tanh": "activation",
+    "lumen_token_gate": "token input", "lumen_add_cast": "token input", "lumen_cols_cast": "delta rule: low-rank inputs",
+    "lumen_delta_rule": "delta rule: recurrence", "lumen_head_norm_gate": "delta rule: norm + gate",
 }
 
 
@@ -180,7 +220,8 @@ def measure(config, batch, steps, warmup, seed=0):
             "prompt_us_by_class": prompt_classes, "decode_us_by_class": decode_classes, "window": window}
 
 
-DESIGNS = {"dabevik": (SIZES, dabevik_config), "rasezen": (RASEZEN_SIZES, rasezen_config)}
+DESIGNS = {"dabevik": (SIZES, dabevik_config), "rasezen": (RASEZEN_SIZES, rasezen_config),
+           "lebelix": (LEBELIX_SIZES, lebelix_config)}
 
 
 def sizes_of(design):
@@ -214,7 +255,7 @@ def steps_main(argv=None) -> int:
     from .engine import Engine, StepEntry
     from .sampling import SamplingConfig
     ap = argparse.ArgumentParser(prog="lumenllm_b200.compare")
-    ap.add_argument("--design", default="dabevik", choices=["dabevik", "rasezen", "qwen3"])
+    ap.add_argument("--design", default="dabevik", choices=sorted(DESIGNS) + ["qwen3"])
     ap.add_argument("--sizes-of", default=None, choices=sorted(DESIGNS),
                     help="with --design qwen3: whose table of sizes the twin takes (default dabevik)")
     ap.add_argument("--kind", default="decode", choices=["prompt", "decode"])

@@ -34,6 +34,12 @@
 // page once that has arrived. One kernel, and one wait for a kernel ahead, fewer on the step's
 // path; the first pages are requested before the wait as ever.
 //
+// Options (AdOpt), each a parameter: `chunk` > 0 limits the query's sight to the keys of its own run
+// of `chunk` positions counted from the sequence's start; `cap_mul` > 0 caps a score s as
+// softcap * tanh(s / softcap); `sink` adds exp(0) to the softmax's denominator (a key of score 0
+// that has no value), once, where the segments' sums have come together; `gate` multiplies the
+// output by sigmoid of some columns of a projection that arrives as float32 partial sums.
+//
 // Scratch: part_o [B, nq, max_segs, D] and part_ml [B, nq, max_segs, 2] float32.
 #include "common.cuh"
 #include "mma_utils.cuh"
@@ -54,10 +60,11 @@ struct SegPlan {
     __device__ __forceinline__ int first(int seg) const { return pg_lo + seg * per + min(seg, rem); }
     __device__ __forceinline__ int count(int seg) const { return per + (seg < rem ? 1 : 0); }
 };
-__device__ __forceinline__ SegPlan seg_plan(int p, int window, int seg_pages) {
+__device__ __forceinline__ SegPlan seg_plan(int p, int window, int seg_pages, int chunk) {
     SegPlan s;
     s.lo = 0;
     if (window > 0 && p - window + 1 > 0) s.lo = p - window + 1;
+    if (chunk > 0) s.lo = max(s.lo, (p / chunk) * chunk);
     s.pg_lo = s.lo / LUMEN_PAGE;
     s.pg_hi = p / LUMEN_PAGE;
     const int np = s.pg_hi - s.pg_lo + 1;
@@ -90,6 +97,32 @@ struct AdQkv {
     __nv_bfloat16* vcache;
 };
 
+struct AdOpt {
+    int chunk;              // 0: none
+    float cap_pre, cap_mul; // capped scores (cap_mul > 0): cap_mul * tanh(raw score * cap_pre), in units of log 2
+    int sink;               // 1: the denominator has one more term exp(0)
+    const float* gate;      // partial sums [gS][B][g_width]; columns g_col0 + head * D + e; null: none
+    int gS;
+    long long g_split_stride;
+    int g_width, g_col0;
+};
+// tanh(x) = 1 - 2 / (1 + e^(2x)); right at both ends (e^(2x) 0 or inf).
+__device__ __forceinline__ float ad_tanh(float x) {
+    return 1.0f - __fdividef(2.0f, 1.0f + ad_ex2(x * 2.8853900817779268f));
+}
+// sigmoid of the gate's four columns for values e .. e + 3 of (sequence b, head); ones without a gate
+__device__ __forceinline__ float4 ad_gate4(const AdOpt& opt, int b, int head, int e, int D) {
+    if (!opt.gate) return make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    const float* g = opt.gate + (size_t)b * opt.g_width + opt.g_col0 + head * D + e;
+    float z[4] = {g[0], g[1], g[2], g[3]};
+    for (int sp = 1; sp < opt.gS; ++sp) {
+        const float* gs = g + (size_t)sp * opt.g_split_stride;
+        z[0] += gs[0]; z[1] += gs[1]; z[2] += gs[2]; z[3] += gs[3];
+    }
+    return make_float4(1.0f / (1.0f + expf(-z[0])), 1.0f / (1.0f + expf(-z[1])), 1.0f / (1.0f + expf(-z[2])),
+                       1.0f / (1.0f + expf(-z[3])));
+}
+
 template <int D, int AD_STAGES>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
@@ -97,7 +130,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
                    int max_segs, int seg_pages, int* __restrict__ err, int* __restrict__ counters,
-                   __nv_bfloat16* __restrict__ out, const AdQkv f) {
+                   __nv_bfloat16* __restrict__ out, const AdQkv f, const AdOpt opt) {
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
     __shared__ __align__(16) __nv_bfloat16 s_q[16 * D];     // the group's query heads, when made here
     extern __shared__ __align__(1024) unsigned char smem[];   // [stages][K tile, V tile]
@@ -108,7 +141,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
     const int seg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int p = seq_pos[b];                   // written before the step's first kernel
-    const SegPlan plan = seg_plan(p, window, seg_pages);
+    const SegPlan plan = seg_plan(p, window, seg_pages, opt.chunk);
     if (seg >= plan.nseg) return;
     const int lo = plan.lo, pg_a = plan.first(seg), npages = plan.count(seg), pg_hi = plan.pg_hi;
 
@@ -242,8 +275,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             for (int i = 0; i < 2; ++i) {
                 const int j = jbase + 8 * nt + 2 * t + i;
                 const bool valid = (j >= lo) && (j <= p);
-                s[nt][i] = valid ? s[nt][i] * scale : -INFINITY;
-                s[nt][2 + i] = valid ? s[nt][2 + i] * scale : -INFINITY;
+                if (opt.cap_mul > 0.0f) {
+                    s[nt][i] = valid ? opt.cap_mul * ad_tanh(s[nt][i] * opt.cap_pre) : -INFINITY;
+                    s[nt][2 + i] = valid ? opt.cap_mul * ad_tanh(s[nt][2 + i] * opt.cap_pre) : -INFINITY;
+                } else {
+                    s[nt][i] = valid ? s[nt][i] * scale : -INFINITY;
+                    s[nt][2 + i] = valid ? s[nt][2 + i] * scale : -INFINITY;
+                }
                 mx0 = fmaxf(mx0, s[nt][i]);
                 mx1 = fmaxf(mx1, s[nt][2 + i]);
             }
@@ -350,10 +388,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
         const size_t head = (size_t)b * nq + (size_t)kvh * G + row;
         if (single) {
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / (opt.sink ? l + ad_ex2(-M) : l);
+            const float4 gt = ad_gate4(opt, b, kvh * G + row, e, D);
             uint2 w2;
-            w2.x = pack_bf16(acc.x * inv, acc.y * inv);
-            w2.y = pack_bf16(acc.z * inv, acc.w * inv);
+            w2.x = pack_bf16(acc.x * inv * gt.x, acc.y * inv * gt.y);
+            w2.y = pack_bf16(acc.z * inv * gt.z, acc.w * inv * gt.w);
             *reinterpret_cast<uint2*>(out + head * D + e) = w2;
         } else {
             const size_t pi = head * max_segs + seg;
@@ -400,10 +439,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             L = L * a + ml.y * f;
             M = mn;
         }
-        const float inv = 1.0f / L;
+        const float inv = 1.0f / (opt.sink ? L + ad_ex2(-M) : L);
+        const float4 gt = ad_gate4(opt, b, kvh * G + row, e, D);
         uint2 w2;
-        w2.x = pack_bf16(acc.x * inv, acc.y * inv);
-        w2.y = pack_bf16(acc.z * inv, acc.w * inv);
+        w2.x = pack_bf16(acc.x * inv * gt.x, acc.y * inv * gt.y);
+        w2.y = pack_bf16(acc.z * inv * gt.z, acc.w * inv * gt.w);
         *reinterpret_cast<uint2*>(out + head * D + e) = w2;
     }
 }
@@ -413,11 +453,12 @@ template <typename TOut>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
                                            const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_pos, TOut* __restrict__ out,
-                                           int nq, int D, int window, int max_segs, int seg_pages) {
+                                           int nq, int D, int window, int max_segs, int seg_pages,
+                                           const AdOpt opt) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     const int head = blockIdx.x, b = blockIdx.y;
-    const SegPlan plan = seg_plan(seq_pos[b], window, seg_pages);
+    const SegPlan plan = seg_plan(seq_pos[b], window, seg_pages, opt.chunk);
     if (plan.nseg == 1) return; // a single segment: the first kernel has written the result
     const int c0 = 0, c1 = plan.nseg - 1;
     const size_t base = ((size_t)b * nq + head) * max_segs;
@@ -425,12 +466,20 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
     for (int c = c0; c <= c1; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
     float L = 0.0f;
     for (int c = c0; c <= c1; ++c) L += part_ml[(base + c) * 2 + 1] * ad_ex2(part_ml[(base + c) * 2] - M);
+    if (opt.sink) L += ad_ex2(-M);
     const float inv = 1.0f / L;
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
         float acc = 0.0f;
         for (int c = c0; c <= c1; ++c)
             acc += part_o[(base + c) * D + e] * ad_ex2(part_ml[(base + c) * 2] - M);
-        out[((size_t)b * nq + head) * D + e] = from_f32<TOut>(acc * inv);
+        float gt = 1.0f;
+        if (opt.gate) {
+            const float* g = opt.gate + (size_t)b * opt.g_width + opt.g_col0 + head * D + e;
+            float z = g[0];
+            for (int sp = 1; sp < opt.gS; ++sp) z += g[(size_t)sp * opt.g_split_stride];
+            gt = 1.0f / (1.0f + expf(-z));
+        }
+        out[((size_t)b * nq + head) * D + e] = from_f32<TOut>(acc * inv * gt);
     }
 }
 
@@ -439,8 +488,13 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
                               const int* block_table, int bt_stride, const int* seq_pos,
                               void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
                               int d, int window, float scale, int max_segs, int seg_pages,
-                              int* err, int* counters, cudaStream_t stream, const AdQkv& f) {
+                              int* err, int* counters, cudaStream_t stream, const AdQkv& f, AdOpt opt = AdOpt(),
+                              float softcap = 0.0f) {
     if (B <= 0) return 0;
+    if (opt.chunk < 0 || softcap < 0.0f) return LUMEN_ERR_UNSUPPORTED;
+    if (opt.gate && (opt.gS < 1 || opt.g_col0 < 0 || opt.g_col0 + nq * d > opt.g_width)) return LUMEN_ERR_BAD_ARGUMENT;
+    opt.cap_pre = softcap > 0.0f ? scale / softcap : 0.0f;
+    opt.cap_mul = softcap > 0.0f ? softcap * 1.4426950408889634f : 0.0f;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_segs <= 0)
         return LUMEN_ERR_UNSUPPORTED;
     if (B > 65535 || nkv > 65535) return LUMEN_ERR_UNSUPPORTED;
@@ -465,7 +519,7 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
         if (err_ != cudaSuccess) return err_;
         return lumen_launch(kernel, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride,
                             seq_pos, part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
-                            (__nv_bfloat16*)out, f);
+                            (__nv_bfloat16*)out, f, opt);
     };
     if (d == 128) {
         e = deep ? go(attn_decode_kernel<128, 3>, 3, 128) : go(attn_decode_kernel<128, 2>, 2, 128);
@@ -480,7 +534,7 @@ static int attn_decode_launch(const void* q, const void* kcache, const void* vca
     dim3 cgrid(nq, B);
     e = lumen_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream,
                      (const float*)part_o, (const float*)part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window,
-                     max_segs, seg_pages);
+                     max_segs, seg_pages, opt);
     if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -503,6 +557,20 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
     AdQkv f = {};
     return attn_decode_launch(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml, B, nq, nkv,
                               d, window, scale, max_segs, seg_pages, err, counters, stream, f);
+}
+
+// lumen_attn_decode with the options of AdOpt: chunk, softcap (0: none), sink, and a gate of float32
+// partial sums [gS][B][g_width] whose columns g_col0 + head * d + e belong to (head, e).
+LUMEN_API int lumen_attn_decode_opt(const void* q, const void* kcache, const void* vcache,
+                                    const int* block_table, int bt_stride, const int* seq_pos,
+                                    void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
+                                    int d, int window, float scale, int max_segs, int seg_pages, int chunk,
+                                    float softcap, int sink, const float* gate, int gS, long long g_split_stride,
+                                    int g_width, int g_col0, int* err, int* counters, cudaStream_t stream) {
+    AdQkv f = {};
+    AdOpt opt = {chunk, 0.0f, 0.0f, sink, gate, gS, g_split_stride, g_width, g_col0};
+    return attn_decode_launch(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml, B, nq, nkv,
+                              d, window, scale, max_segs, seg_pages, err, counters, stream, f, opt, softcap);
 }
 
 // The same with the rotary kernel's work done by the attention blocks (head size 128). qkv:

@@ -50,6 +50,14 @@
 // A block needs half of an SM's shared memory and half of its tensor memory, so two blocks
 // share an SM and one's softmax runs under the other's products.
 //
+// Options (PtOpt), each a parameter: `chunk` > 0 limits a row's sight to the keys of its own run of
+// `chunk` positions counted from the sequence's start (the pages before the tile's first chunk are
+// not walked at all); with CAP a score s becomes softcap * tanh(s / softcap), the tanh taken as
+// 1 - 2 / (1 + e^(2x)) with the special-function unit's exponential and reciprocal (absolute error
+// about 1e-7, so about softcap * 1e-7 in the score); `sink` starts a row's running sum at exp(0)
+// against the reference 0 (a key of score 0 that has no value); `gate` multiplies the output by
+// sigmoid of some columns of a projection that arrives as float32 partial sums.
+//
 // Page tiles start at multiples of 64 in absolute position, so what a row computes depends
 // only on its own position. Every wait is bounded; when one runs out the block raises the
 // error flag, lets the other roles run out, frees its tensor memory and returns.
@@ -193,13 +201,28 @@ __host__ __device__ constexpr uint32_t pt_idesc(int n, int b_mn) {
            ((uint32_t)(PT_ROWS >> 4) << 24);
 }
 
-template <int D>
+struct PtOpt {
+    int chunk;              // 0: none
+    float cap_pre;          // with CAP: scale / softcap, what a raw score is multiplied by before the tanh
+    int sink;               // 1: the denominator has one more term exp(0)
+    const float* gate;      // partial sums [gS][N][g_width]; columns g_col0 + head * D + e; null: none
+    int gS;
+    long long g_split_stride;
+    int g_width, g_col0;
+};
+
+// tanh(x) = 1 - 2 / (1 + e^(2x)); right at both ends (e^(2x) 0 or inf).
+__device__ __forceinline__ float pt_tanh(float x) {
+    return 1.0f - __fdividef(2.0f, 1.0f + pt_ex2(x * 2.8853900817779268f));
+}
+
+template <int D, bool CAP>
 __global__ void __launch_bounds__(PT_THREADS, 2)
 attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                        const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
                        int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_start,
                        int B, __nv_bfloat16* __restrict__ out, int nq, int nkv, int window,
-                       float scale_log2, int* __restrict__ err) {
+                       float scale_log2, int* __restrict__ err, const PtOpt opt) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;      // one K or V page tile
@@ -248,6 +271,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int pos_last = pos0 + ntok - 1;
     int j_lo = 0;
     if (window > 0 && pos0 - window + 1 > 0) j_lo = pos0 - window + 1;
+    if (opt.chunk > 0) j_lo = max(j_lo, (pos0 / opt.chunk) * opt.chunk);
     const int pg_lo = j_lo / LUMEN_PAGE, pg_hi = pos_last / LUMEN_PAGE;
     const int npages = pg_hi - pg_lo + 1;
     const int* bt = block_table + (size_t)b * bt_stride;
@@ -372,9 +396,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         const int tok = r / G, h = r - tok * G;
         const bool row_ok = tok < ntok && r < TQ * G;
         const int prow = pos0 + tok;                       // absolute position of the row's query
-        const int lorow = (window > 0) ? prow - window + 1 : 0;
+        int lorow = (window > 0) ? prow - window + 1 : 0;
+        if (opt.chunk > 0) lorow = max(lorow, (prow / opt.chunk) * opt.chunk);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
-        float m_ref = -INFINITY, l = 0.0f;
+        // with a sink the row starts as if a key of score 0 had been seen: reference 0, sum exp(0)
+        float m_ref = opt.sink ? 0.0f : -INFINITY, l = opt.sink ? 1.0f : 0.0f;
         bool ok = true;
         for (int it = 0; it < npages; ++it) {
             if (__any_sync(0xffffffffu, *abort_flag != 0)) { ok = false; break; }
@@ -383,6 +409,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             pt_fence_after();
             float s[64];
             pt_ld64(lane_addr + (it & 1) * LUMEN_PAGE, s);
+            if (CAP) {       // capped scores: tanh here, times softcap * log2(e) (scale_log2) below
+#pragma unroll
+                for (int j = 0; j < 64; ++j) s[j] = pt_tanh(s[j] * opt.cap_pre);
+            }
             const int jb = (pg_lo + it) * LUMEN_PAGE;
             const bool full_page = (jb + LUMEN_PAGE - 1 <= prow) && (jb >= lorow);
             if (!__all_sync(0xffffffffu, full_page)) {       // only pages on the diagonal or the window's edge
@@ -465,10 +495,20 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             pt_fence_after();
             const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = out + ((size_t)(n0 + tok) * nq + kvh * G + h) * D;
+            const float* grow = opt.gate ? opt.gate + (size_t)(n0 + tok) * opt.g_width + opt.g_col0 + (kvh * G + h) * D
+                                         : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
                 float ov[32];
                 pt_ld32(lane_addr + O_COL + c0, ov);
+                if (row_ok && grow) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float z = grow[c0 + j];
+                        for (int sp = 1; sp < opt.gS; ++sp) z += grow[(size_t)sp * opt.g_split_stride + c0 + j];
+                        ov[j] *= 1.0f / (1.0f + expf(-z));
+                    }
+                }
                 if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
@@ -494,38 +534,66 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
 // q, out: bfloat16 [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B] (cached length of each
 // sequence before this step); n_tiles = sum over sequences of ceil(q_len / (128 / (nq/nkv))).
+template <int D, bool CAP>
+static cudaError_t pt_go(dim3 grid, cudaStream_t stream, const __nv_bfloat16* qp, const __nv_bfloat16* kp,
+                         const __nv_bfloat16* vp, const int* block_table, int bt_stride, const int* cu_q,
+                         const int* seq_start, int B, void* out, int nq, int nkv, int window, float scale_log2,
+                         int* err, const PtOpt& opt) {
+    const int smem = PT_ROWS * D * 2 + PT_STAGES * 2 * LUMEN_PAGE * D * 2 + 256;
+    auto k = attn_prefill_tc_kernel<D, CAP>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    return lumen_launch(k, grid, dim3(PT_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q,
+                        seq_start, B, (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err, opt);
+}
+
+static int pt_launch(const void* q, const void* kcache, const void* vcache, const int* block_table, int bt_stride,
+                     const int* cu_q, const int* seq_start, int B, int n_tiles, void* out, int nq, int nkv, int d,
+                     int window, float scale, float softcap, int* err, PtOpt opt, cudaStream_t stream) {
+    if (B <= 0 || n_tiles <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || opt.chunk < 0 || softcap < 0.0f)
+        return LUMEN_ERR_UNSUPPORTED;
+    if (opt.gate && (opt.gS < 1 || opt.g_col0 < 0 || opt.g_col0 + nq * d > opt.g_width)) return LUMEN_ERR_BAD_ARGUMENT;
+    if ((long long)n_tiles * nkv > 2147483647LL) return LUMEN_ERR_UNSUPPORTED;
+    dim3 grid(n_tiles * nkv);
+    const bool cap = softcap > 0.0f;
+    // capped: the tanh's argument is score * scale / softcap, and the exponent softcap * log2(e) * tanh
+    const float scale_log2 = (cap ? softcap : scale) * 1.4426950408889634f;
+    opt.cap_pre = cap ? scale / softcap : 0.0f;
+    const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
+    const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
+    const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
+    cudaError_t e;
+#define PT_GO(DD, CC) pt_go<DD, CC>(grid, stream, qp, kp, vp, block_table, bt_stride, cu_q, seq_start, B, out, nq, nkv, \
+                                    window, scale_log2, err, opt)
+    if (d == 128) e = cap ? PT_GO(128, true) : PT_GO(128, false);
+    else if (d == 64) e = cap ? PT_GO(64, true) : PT_GO(64, false);
+    else return LUMEN_ERR_UNSUPPORTED;
+#undef PT_GO
+    if (e != cudaSuccess) return (int)e;
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
 LUMEN_API int lumen_attn_prefill_tc(const void* q, const void* kcache, const void* vcache,
                                     const int* block_table, int bt_stride, const int* cu_q,
                                     const int* seq_start, int B, int n_tiles, void* out, int nq,
                                     int nkv, int d, int window, float scale, int* err,
                                     cudaStream_t stream) {
-    if (B <= 0 || n_tiles <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0) return LUMEN_ERR_UNSUPPORTED;
-    if ((long long)n_tiles * nkv > 2147483647LL) return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid(n_tiles * nkv);
-    const float scale_log2 = scale * 1.4426950408889634f;
-    const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
-    const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
-    const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
-    cudaError_t e;
-    if (d == 128) {
-        const int smem = PT_ROWS * 128 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 128 * 2 + 256;
-        auto k = attn_prefill_tc_kernel<128>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        e = lumen_launch(k, grid, dim3(PT_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q,
-                         seq_start, B, (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err);
-    } else if (d == 64) {
-        const int smem = PT_ROWS * 64 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 64 * 2 + 256;
-        auto k = attn_prefill_tc_kernel<64>;
-        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        e = lumen_launch(k, grid, dim3(PT_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q,
-                         seq_start, B, (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err);
-    } else {
-        return LUMEN_ERR_UNSUPPORTED;
-    }
-    if (e != cudaSuccess) return (int)e;
-    LUMEN_LAUNCH_CHECK();
-    return 0;
+    PtOpt opt = {};
+    return pt_launch(q, kcache, vcache, block_table, bt_stride, cu_q, seq_start, B, n_tiles, out, nq, nkv, d, window,
+                     scale, 0.0f, err, opt, stream);
+}
+
+// The same with the options of PtOpt: chunk, softcap (0: none), sink, and a gate of float32 partial sums
+// [gS][N][g_width] whose columns g_col0 + head * d + e belong to (head, e).
+LUMEN_API int lumen_attn_prefill_tc_opt(const void* q, const void* kcache, const void* vcache,
+                                        const int* block_table, int bt_stride, const int* cu_q,
+                                        const int* seq_start, int B, int n_tiles, void* out, int nq,
+                                        int nkv, int d, int window, float scale, int chunk, float softcap,
+                                        int sink, const float* gate, int gS, long long g_split_stride,
+                                        int g_width, int g_col0, int* err, cudaStream_t stream) {
+    PtOpt opt = {chunk, 0.0f, sink, gate, gS, g_split_stride, g_width, g_col0};
+    return pt_launch(q, kcache, vcache, block_table, bt_stride, cu_q, seq_start, B, n_tiles, out, nq, nkv, d, window,
+                     scale, softcap, err, opt, stream);
 }

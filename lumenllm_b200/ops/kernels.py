@@ -1114,9 +1114,22 @@ DECODE_MAX_SEGS = 32
 DECODE_SEG_PAGES = 4
 
 
-def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
+def _gate_args(gate, rows, what):
+    """(tensor, splits, split stride, width) of a gate that arrives as float32 partial sums [N, W] or
+    [S, N, W]; zeros without one."""
+    if gate is None:
+        return None, 0, 0, 0
+    gate, gS = _partials(gate, what)
+    if gate.shape[1] != rows:
+        raise KernelError(f"{what}: the gate has one row a token")
+    return gate, gS, gate.shape[1] * gate.shape[2], gate.shape[2]
+
+
+def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale, chunk=0, softcap=0.0, sink=False,
+                gate=None, gate_col=0):
     """Split-KV decode attention, bfloat16, swizzled cache, head size 64 or 128, at most
-    16 query heads per kv head. q [B, nq, d]; seq_pos int32 [B]: each query's position."""
+    16 query heads per kv head. q [B, nq, d]; seq_pos int32 [B]: each query's position.
+    `chunk`, `softcap`, `sink`, `gate` and `gate_col` as in attn_generic_opt."""
     B, nq, d = q.shape
     nkv = kcache.shape[1]
     require(q, BF16, "attn_decode.q")
@@ -1133,6 +1146,16 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     part_o = torch.empty((B, nq, max_segs, d), dtype=F32, device=q.device)
     part_ml = torch.empty((B, nq, max_segs, 2), dtype=F32, device=q.device)
     counters = _decode_counters(q.device) if B * nkv <= _COUNTERS else None
+    if chunk or softcap or sink or gate is not None:
+        gate, gS, gstride, gW = _gate_args(gate, B, "attn_decode.gate")
+        f = fn("attn_decode", "lumen_attn_decode_opt",
+               [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float,
+                c_int, P, c_int, c_longlong, c_int, c_int, P, P, P])
+        check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
+                ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_segs, seg_pages,
+                int(chunk), float(softcap or 0.0), 1 if sink else 0, ptr(gate), gS, gstride, gW, int(gate_col),
+                ptr(error_flag(q.device)), ptr(counters), stream_ptr()), "attn_decode_opt")
+        return out
     f = fn("attn_decode", "lumen_attn_decode",
            [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P, P, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
@@ -1190,14 +1213,16 @@ def attn_decode_qkv(qkv, q_norm_w, k_norm_w, eps, cs, rotary_dim, kcache, vcache
 
 
 def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale,
-                 tensor_memory=True, n_seqs=None):
+                 tensor_memory=True, n_seqs=None, chunk=0, softcap=0.0, sink=False, gate=None, gate_col=0):
     """Causal flash attention for sequences that bring q_lens[b] tokens each (host list),
     bfloat16, swizzled cache, head size 64 or 128, at most 16 query heads per kv head.
     q [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B]. With tensor_memory the tcgen05
     kernel (128 rows a block, S and O in tensor memory), else the mma.sync kernel (64 rows).
     With q_lens None and n_seqs = B the host need not know how the N tokens are divided (a
     captured step does not): enough blocks are launched for any division, every block finds
-    its sequence and tile from cu_q on the device, and the blocks left over return at once."""
+    its sequence and tile from cu_q on the device, and the blocks left over return at once.
+    `chunk`, `softcap`, `sink`, `gate` and `gate_col` as in attn_generic_opt (tensor-memory kernel
+    only)."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
     B = len(q_lens) if q_lens is not None else int(n_seqs)
@@ -1216,6 +1241,18 @@ def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window
     # sum of ceil(q_b / tq) over any division of N tokens into B sequences is at most N // tq + B
     n_tiles = sum((n + tq - 1) // tq for n in q_lens) if q_lens is not None else N // tq + B
     out = torch.empty_like(q)
+    if chunk or softcap or sink or gate is not None:
+        if not tensor_memory:
+            raise KernelError("attn_prefill: the options are the tensor-memory kernel's")
+        gate, gS, gstride, gW = _gate_args(gate, N, "attn_prefill.gate")
+        f = fn("attn_prefill_tc", "lumen_attn_prefill_tc_opt",
+               [P, P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_int,
+                P, c_int, c_longlong, c_int, c_int, P, P])
+        check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(cu_q),
+                ptr(seq_start), B, n_tiles, ptr(out), nq, nkv, d, int(window), float(scale), int(chunk),
+                float(softcap or 0.0), 1 if sink else 0, ptr(gate), gS, gstride, gW, int(gate_col),
+                ptr(error_flag(q.device)), stream_ptr()), "attn_prefill_opt")
+        return out
     f = fn("attn_prefill_tc" if tensor_memory else "attn_prefill",
            "lumen_attn_prefill_tc" if tensor_memory else "lumen_attn_prefill",
            [P, P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P, P])

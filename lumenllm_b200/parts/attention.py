@@ -138,19 +138,19 @@ def causal_attention(q, kc, vc, table, ctx, k_layout, v_layout, window, scale, c
     `chunk`, `softcap`, `sink` and `gate` are the options of ops.kernels.attn_generic_opt."""
     nq, d = q.shape[1], q.shape[2]
     nkv, dv = kc.shape[1], vc.shape[3]
-    if chunk or softcap or sink or gate is not None:
-        return K.attn_generic_opt(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, window, scale, layout=k_layout,
-                                  v_layout=v_layout, chunk=chunk, softcap=softcap, sink=sink, gate=gate,
-                                  gate_col=gate_col)
+    opts = dict(chunk=chunk, softcap=softcap, sink=sink, gate=gate, gate_col=gate_col)
     fast = (k_layout == K.LAYOUT_SW128 and v_layout == K.LAYOUT_SW128 and q.dtype == torch.bfloat16
             and d == dv and d in (64, 128) and nq // nkv <= 16)
     if fast and ctx.is_decode:
-        return K.attn_decode(q, kc, vc, table, ctx.cache_pos, window, scale)
+        return K.attn_decode(q, kc, vc, table, ctx.cache_pos, window, scale, **opts)
     if fast:
         # a captured step is replayed for other divisions of its tokens than the one it was
         # captured with: the kernel then takes the division from the device alone
         q_lens = None if ctx.extras.get("captured") else ctx.q_lens
-        return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, q_lens, window, scale, n_seqs=ctx.B)
+        return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, q_lens, window, scale, n_seqs=ctx.B, **opts)
+    if chunk or softcap or sink or gate is not None:
+        return K.attn_generic_opt(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, window, scale, layout=k_layout,
+                                  v_layout=v_layout, **opts)
     return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, window, scale, layout=k_layout,
                           v_layout=v_layout)
 

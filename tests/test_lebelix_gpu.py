@@ -157,7 +157,12 @@ ATTENTIONS = [attention(4, 2, 16, 24, 0.3, size=9, rot=8, softcap=5.0),
               attention(2, 2, 64, 128, 0.15, size=64, rot=16, softcap=30.0),   # chunks of exactly a page
               attention(5, 5, 24, 8, 0.5, size=1, rot=24),                  # every query sees itself only
               attention(12, 1, 20, 10, 0.4, size=130, rot=4, softcap=50.0),
-              attention(4, 2, 128, 128, 0.09, size=100, rot=64, softcap=20.0)]
+              attention(4, 2, 128, 128, 0.09, size=100, rot=64, softcap=20.0),
+              # key and value sizes that the tensor-core kernels of a bfloat16 run take
+              attention(4, 1, 64, 64, 0.125, size=96, rot=32, softcap=50.0),
+              attention(2, 2, 64, 64, 0.2, size=200),                       # uncapped: sink and gate alone
+              attention(16, 1, 128, 128, 0.09, rot=128, softcap=3.0),       # no mask, sixteen heads a kv head
+              attention(3, 3, 128, 128, 0.1, size=64)]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -172,12 +177,14 @@ def test_attention_part(m, dtype):
     close(got, ref, dtype)
 
 
+@pytest.mark.parametrize("d", [32, 64])
 @pytest.mark.parametrize("dtype", [F32, BF16])
-def test_the_sink_takes_weight_and_the_cap_bounds_scores(dtype):
+def test_the_sink_takes_weight_and_the_cap_bounds_scores(dtype, d):
     """Keys that all point away from the queries: nearly all weight goes to the sink, and the output
     is small, where an ordinary softmax would give an average of the values. Then loud queries and
     keys with a low cap: the weights stay spread where uncapped scores would pick one key."""
-    H, d, D, T = 2, 32, 64, 50
+    H, T = 2, 50
+    D = H * d
     m = attention(H, H, d, d, 1.0, size=40, softcap=30.0)
 
     def away(w):
@@ -213,9 +220,10 @@ def loud_pair(w, D, shift):
     w["l0.mix.k"] = torch.roll(torch.eye(D), shift, dims=0).to(BF16)
 
 
+@pytest.mark.parametrize("d", [32, 64])
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("dtype", [F32, BF16])
-def test_one_loud_key_at_every_edge_of_a_chunk(dtype, decode):
+def test_one_loud_key_at_every_edge_of_a_chunk(dtype, decode, d):
     """One earlier token is made loud so that its KEY points where the last QUERY points: this single
     key takes nearly all of the query's weight where it is in sight and none where it is not: on both
     sides of the chunk's edge, at page borders inside the chunk, at the chunk's far end among
@@ -223,7 +231,8 @@ def test_one_loud_key_at_every_edge_of_a_chunk(dtype, decode):
     size that differs by one: the plain result under it must be far from the right one, else the
     case would show nothing. Chunks are counted from the sequence's first token also when the
     sequence came in portions."""
-    H, d, D = 2, 32, 64
+    H = 2
+    D = H * d
     size = 150
     T = 2 * size + 140                   # the last query is the 140th token of the third chunk
     m = attention(H, H, d, d, 1.0, size=size)
