@@ -122,6 +122,7 @@ CLASSES = {
     "lumen_moe_group": "experts: route + group",
     "lumen_qkv_head_norm_store": "q/k norm + cache write", "lumen_attn_generic_opt": "attention (general kernel)",
     "lumen_attn_prefill_tc_opt": "attention", "lumen_attn_decode_opt": "attention",
+    "lumen_attn_latent": "attention (latent kernel)",
     "lumen_latent_store": "latent: norm + cache write", "lumen_latent_query": "latent: queries into the latent space",
     "lumen_head_product": "latent: values out of the latent space", "lumen_gelu_tanh": "activation",
     "lumen_token_gate": "token input", "lumen_add_cast": "token input", "lumen_cols_cast": "delta rule: low-rank inputs",

@@ -30,6 +30,7 @@ MODULES = {
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"]),
     "gemm_tc": (["gemm_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
+    "attn_latent": (["attn_latent.cu"], ["common.cuh", "mma_utils.cuh"]),
     "layer_ops": (["layer_ops.cu"], ["common.cuh"]),
     "attn_talk": (["attn_talk.cu"], ["common.cuh", "mma_utils.cuh"]),
     "ssm": (["ssm.cu"], ["common.cuh"]),

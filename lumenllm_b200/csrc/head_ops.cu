@@ -171,13 +171,14 @@ LUMEN_API int lumen_latent_store(const float* u, int n_split, long long split_st
 
 // ---------------------------------------------------------------- latent attention: the query in the latent space
 // Row n of the query projection holds H heads of [d plain | r rotated]. out[n, h] =
-// [ sum_j q[n, h, j] Uk[h d + j, :]  (R numbers) | the r rotated numbers ], float32. Uk is stored
-// [H d, R]. A block takes LQ_TOK tokens of one head; a thread a latent coordinate.
+// [ sum_j q[n, h, j] Uk[h d + j, :]  (R numbers) | the r rotated numbers ], float32 or bfloat16. Uk is
+// stored [H d, R]. A block takes LQ_TOK tokens of one head and every gridDim.z-th run of 128 latent
+// coordinates; a thread a latent coordinate. Block z = 0 also writes the rotated numbers.
 #define LQ_TOK 8
-template <typename TW>
+template <typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int W, const TW* __restrict__ uk, int H,
-                    int d, int r, int R, const float2* __restrict__ cs, int rot, float* __restrict__ out, int N) {
+                    int d, int r, int R, const float2* __restrict__ cs, int rot, TO* __restrict__ out, int N) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float qs[];          // [LQ_TOK][d]
@@ -189,7 +190,7 @@ latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int
     }
     __syncthreads();
     const TW* w = uk + (size_t)h * d * R;
-    for (int e = tid; e < R; e += 128) {
+    for (int e = blockIdx.z * 128 + tid; e < R; e += 128 * gridDim.z) {
         float acc[LQ_TOK];
 #pragma unroll
         for (int t = 0; t < LQ_TOK; ++t) acc[t] = 0.0f;
@@ -200,8 +201,9 @@ latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int
         }
 #pragma unroll
         for (int t = 0; t < LQ_TOK; ++t)
-            if (t < nt) out[((size_t)(n0 + t) * H + h) * (R + r) + e] = acc[t];
+            if (t < nt) out[((size_t)(n0 + t) * H + h) * (R + r) + e] = from_f32<TO>(acc[t]);
     }
+    if (blockIdx.z != 0) return;
     const int half = rot >> 1;
     for (int i = tid; i < nt * r; i += 128) {
         const int t = i / r, e = i - t * r;
@@ -213,33 +215,35 @@ latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int
             const float other = parts_sum(src + (e < half ? e + half : e - half), S, split_stride);
             x = e < half ? x * c_s.x - other * c_s.y : x * c_s.x + other * c_s.y;
         }
-        out[((size_t)(n0 + t) * H + h) * (R + r) + R + e] = x;
+        out[((size_t)(n0 + t) * H + h) * (R + r) + R + e] = from_f32<TO>(x);
     }
 }
 
 LUMEN_API int lumen_latent_query(const float* q, int n_split, long long split_stride, int W, const void* uk,
-                                 int uk_is_bf16, int H, int d, int r, int R, const float* cs, int rot, float* out, int N,
-                                 cudaStream_t stream) {
+                                 int uk_is_bf16, int H, int d, int r, int R, const float* cs, int rot, void* out,
+                                 int out_is_bf16, int N, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (H <= 0 || H > 65535 || d <= 0 || r < 0 || R <= 0 || rot < 0 || rot > r || (rot & 1) || W < H * (d + r) ||
         n_split < 1 || (size_t)LQ_TOK * d * sizeof(float) > 48 * 1024)
         return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid((N + LQ_TOK - 1) / LQ_TOK, H);
+    dim3 grid((N + LQ_TOK - 1) / LQ_TOK, H, (R + 127) / 128);
     const size_t smem = (size_t)LQ_TOK * d * sizeof(float);
-    if (uk_is_bf16)
-        lumen_launch(latent_query_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, q, n_split, (size_t)split_stride,
-                     W, (const __nv_bfloat16*)uk, H, d, r, R, (const float2*)cs, rot, out, N);
-    else
-        lumen_launch(latent_query_kernel<float>, grid, dim3(128), smem, stream, q, n_split, (size_t)split_stride, W,
-                     (const float*)uk, H, d, r, R, (const float2*)cs, rot, out, N);
+#define LQ_LAUNCH(TW, TO)                                                                                            \
+    lumen_launch(latent_query_kernel<TW, TO>, grid, dim3(128), smem, stream, q, n_split, (size_t)split_stride, W,    \
+                 (const TW*)uk, H, d, r, R, (const float2*)cs, rot, (TO*)out, N)
+    if (uk_is_bf16 && out_is_bf16) LQ_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (uk_is_bf16) LQ_LAUNCH(__nv_bfloat16, float);
+    else if (out_is_bf16) LQ_LAUNCH(float, __nv_bfloat16);
+    else LQ_LAUNCH(float, float);
+#undef LQ_LAUNCH
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
 
 // ---------------------------------------------------------------- a product of its own for every head
 // out[n, h, e] = sum_j x[n, h, j] w[h E + e, j]: x float32 [N, H, J], w [H E, J], out [N, H E] in
-// the run's type. A block takes HP_TOK tokens of one head; a warp an output coordinate at a
-// time, its lanes along j.
+// the run's type. A block takes HP_TOK tokens of one head and every gridDim.z-th run of 8 output
+// coordinates; a warp an output coordinate at a time, its lanes along j.
 #define HP_TOK 8
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256)
@@ -256,7 +260,7 @@ head_product_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* _
     }
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31;
-    for (int e = warp; e < E; e += 8) {
+    for (int e = blockIdx.z * 8 + warp; e < E; e += 8 * gridDim.z) {
         const TW* wr = w + ((size_t)h * E + e) * J;
         float acc[HP_TOK];
 #pragma unroll
@@ -278,7 +282,9 @@ LUMEN_API int lumen_head_product(const float* x, const void* w, int w_is_bf16, v
     if (N <= 0) return 0;
     if (H <= 0 || H > 65535 || J <= 0 || E <= 0 || (size_t)HP_TOK * J * sizeof(float) > 48 * 1024)
         return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid((N + HP_TOK - 1) / HP_TOK, H);
+    // few tokens: a head's outputs are spread over more blocks, so that the step fills the device
+    const int gz = N <= 8 * HP_TOK ? min(8, (E + 7) / 8) : 1;
+    dim3 grid((N + HP_TOK - 1) / HP_TOK, H, gz);
     const size_t smem = (size_t)HP_TOK * J * sizeof(float);
     if (w_is_bf16 && out_is_bf16)
         lumen_launch(head_product_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), smem, stream, x,

@@ -780,11 +780,11 @@ def latent_store(u, col, rank, rot_width, norm_w, eps, cs, rotary_dim, cache_pos
             block_table.stride(0), ptr(cache), _is_bf16(cache), N, stream_ptr()), "latent_store")
 
 
-def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim):
+def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim, out_dtype=F32):
     """Queries carried into the latent space: q float32 [N, W] or partial sums, rows of `heads` heads
-    of [d | rot_width]; up_k [heads * d, rank] (the keys' up-projection). Returns float32 [N, heads,
-    rank + rot_width]: sum_j q[h, j] up_k[h d + j, :], then the rot_width values with the first
-    rotary_dim rotated by `cs`."""
+    of [d | rot_width]; up_k [heads * d, rank] (the keys' up-projection). Returns [N, heads,
+    rank + rot_width] in out_dtype (float32 or bfloat16): sum_j q[h, j] up_k[h d + j, :], then the
+    rot_width values with the first rotary_dim rotated by `cs`."""
     q, S = _partials(q, "latent_query.q")
     N, W = q.shape[1], q.shape[2]
     if tuple(up_k.shape) != (heads * d, rank) or not up_k.is_contiguous() or W < heads * (d + rot_width):
@@ -794,11 +794,54 @@ def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim):
         require(cs, F32, "latent_query.cs")
         if tuple(cs.shape) != (N, rotary_dim // 2, 2):
             raise KernelError(f"latent_query: angles {tuple(cs.shape)} do not fit {N} tokens and {rotary_dim}")
-    out = torch.empty((N, heads, rank + rot_width), dtype=F32, device=q.device)
+    out = torch.empty((N, heads, rank + rot_width), dtype=out_dtype, device=q.device)
     f = fn("head_ops", "lumen_latent_query",
-           [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, P])
+           [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, c_int, P])
     check(f(ptr(q), S, N * W, W, ptr(up_k), _is_bf16(up_k), int(heads), int(d), int(rot_width), int(rank),
-            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(out), N, stream_ptr()), "latent_query")
+            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(out), _is_bf16(out), N, stream_ptr()), "latent_query")
+    return out
+
+
+ATTN_LATENT_ROWS = 64      # (token, head) rows a block of attn_latent takes
+
+
+def attn_latent_takes(width, value_dim, dtype) -> bool:
+    """Whether attn_latent runs a bfloat16 latent cache with rows of `width` values, the first
+    `value_dim` of them the value: widths that are multiples of 16 and fit a block's shared memory
+    with the queries and two key tiles, values that are multiples of 8 up to 512."""
+    if dtype != BF16:
+        return False
+    f = fn("attn_latent", "lumen_attn_latent_takes", [c_int, c_int])
+    return bool(f(int(width), int(value_dim)))
+
+
+def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, window, scale, n_seqs=None):
+    """Causal attention over a latent cache on the tensor cores (mma.sync): q bfloat16 [N, H, W],
+    already in the cache's space; cache bfloat16 [pages, 1, PAGE, W] (plain tiles), a row the key of
+    every head and its first value_dim numbers the value of every head; a query at position p sees
+    key j if 0 <= p - j < window (window 0: every earlier key). Returns float32 [N, H, value_dim].
+    Prompts and decoded tokens alike; q_lens (host list) or, with q_lens None, n_seqs = B as in
+    attn_prefill."""
+    N, H, W = q.shape
+    B = len(q_lens) if q_lens is not None else int(n_seqs)
+    require(q, BF16, "attn_latent.q")
+    require(cache, BF16, "attn_latent.cache")
+    for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (seq_start, "seq_start")):
+        require(t, I32, f"attn_latent.{nm}")
+    if tuple(cache.shape[1:]) != (1, PAGE, W):
+        raise KernelError(f"attn_latent: cache {tuple(cache.shape)} does not fit rows of {W}")
+    if cu_q.numel() < B + 1 or seq_start.numel() < B or block_table.shape[0] < B or \
+            (q_lens is not None and sum(q_lens) != N):
+        raise KernelError("attn_latent: metadata does not match the batch")
+    rows = ATTN_LATENT_ROWS
+    # sum of ceil(q_b H / rows) over any division of N tokens into B sequences is at most N H // rows + B
+    n_tiles = sum((n * H + rows - 1) // rows for n in q_lens) if q_lens is not None else N * H // rows + B
+    out = torch.empty((N, H, int(value_dim)), dtype=F32, device=q.device)
+    f = fn("attn_latent", "lumen_attn_latent",
+           [P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P, P])
+    check(f(ptr(q), ptr(cache), ptr(block_table), block_table.stride(0), ptr(cu_q), ptr(seq_start), B, n_tiles,
+            ptr(out), H, W, int(value_dim), int(window), float(scale), ptr(error_flag(q.device)), stream_ptr()),
+          "attn_latent")
     return out
 
 

@@ -12,8 +12,10 @@ softmax; o = ctx Wo^T.
 The cache keeps [c | rotated key part] per token and nothing per head (CacheNeed.values_in_keys:
 one kv head whose rows are R + r wide and whose values are the rows' first R numbers). A query
 head is carried into the latent space, q_plain Uk_h (kernels.latent_query), scores and weighted
-sums are taken over the cached rows by the general attention kernel, and the sums come back through
-Uv_h (kernels.head_product); nothing of a key or value is ever expanded. With `shares_cache` the
+sums are taken over the cached rows (kernels.attn_latent on the tensor cores in bfloat16, where a
+block's rows are (token, head) pairs that share every cached row; the general attention kernel in
+float32 and for widths the other does not take), and the sums come back through Uv_h
+(kernels.head_product); nothing of a key or value is ever expanded. With `shares_cache` the
 part has no Wdkv and reads the cache of the entry the schedule names, with its own Uk, Uv, queries
 and window; `cache_window` is what the cache must keep in sight (the widest window of its readers).
 """
@@ -93,8 +95,16 @@ class LatentAttention:
         if entry.writes_cache and not self.shares_cache:
             K.latent_store(u, self.H * (self.d + self.r), self.R, self.r, self.c_norm, self.eps, cs, rot,
                            ctx.cache_pos, ctx.tok_seq, table, kc)
-        q = K.latent_query(u, self.uk, self.H, self.d, self.r, self.R, cs, rot)
-        mixed = K.attn_generic_opt(q, kc, None, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
-                                   layout=LAYOUT_LINEAR, values_in_keys=True, value_dim=self.R)
+        if K.attn_latent_takes(self.R + self.r, self.R, kc.dtype):
+            # bfloat16: queries rounded once they are in the latent space, scores and sums on the tensor cores
+            q = K.latent_query(u, self.uk, self.H, self.d, self.r, self.R, cs, rot, out_dtype=torch.bfloat16)
+            # a captured step is replayed for other divisions of its tokens than the one it was captured with
+            q_lens = None if ctx.extras.get("captured") else ctx.q_lens
+            mixed = K.attn_latent(q, kc, table, ctx.cu_q, ctx.seq_start, q_lens, self.R, self.window, self.scale,
+                                  n_seqs=ctx.B)
+        else:
+            q = K.latent_query(u, self.uk, self.H, self.d, self.r, self.R, cs, rot)
+            mixed = K.attn_generic_opt(q, kc, None, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
+                                       layout=LAYOUT_LINEAR, values_in_keys=True, value_dim=self.R)
         out = K.head_product(mixed, self.uv, self.runtime.dtype)
         return self.o(out, split_ok=True, add_to=residual)

@@ -267,7 +267,12 @@ LATENTS = [latent(2, 8, 16, 24, 40, 0.2, size=11, rot=8),
            latent(3, 16, 32, 8, 96, 0.25, size=70, rot=32),
            latent(1, 64, 64, 128, 192, 0.1, size=64, rot=64),
            latent(5, 12, 4, 20, 36, 0.3, size=1, rot=4),
-           latent(2, 32, 16, 48, 52, 0.2, size=300)]                  # no rotation at all
+           latent(2, 32, 16, 48, 52, 0.2, size=300),                  # no rotation at all
+           # widths the tensor-core kernel takes: an odd number of 16-value steps and heads that do not
+           # divide a block's rows; a latent wider than 256; more heads than a block has rows
+           latent(5, 16, 16, 32, 160, 0.2, size=45, rot=16),
+           latent(3, 32, 32, 64, 320, 0.1, size=130, rot=32),
+           latent(70, 8, 16, 8, 48, 0.2, size=33, rot=8)]
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
