@@ -124,7 +124,7 @@ CLASSES = {
     "lumen_attn_prefill_tc_opt": "attention", "lumen_attn_decode_opt": "attention",
     "lumen_attn_latent": "attention (latent kernel)",
     "lumen_latent_store": "latent: norm + cache write", "lumen_latent_query": "latent: queries into the latent space",
-    "lumen_head_product": "latent: values out of the latent space", "lumen_gelu_tanh": "activation",
+    "lumen_head_product": "latent: values out of the latent space", "lumen_head_gemm": "latent: products of every head", "lumen_gelu_tanh": "activation",
     "lumen_token_gate": "token input", "lumen_add_cast": "token input", "lumen_cols_cast": "delta rule: low-rank inputs",
     "lumen_delta_rule": "delta rule: recurrence", "lumen_head_norm_gate": "delta rule: norm + gate",
 }

@@ -34,7 +34,7 @@ MODULES = {
     "layer_ops": (["layer_ops.cu"], ["common.cuh"]),
     "attn_talk": (["attn_talk.cu"], ["common.cuh", "mma_utils.cuh"]),
     "ssm": (["ssm.cu"], ["common.cuh"]),
-    "head_ops": (["head_ops.cu"], ["common.cuh"]),
+    "head_ops": (["head_ops.cu"], ["common.cuh", "mma_utils.cuh"]),
     "delta_rule": (["delta_rule.cu"], ["common.cuh"]),
     "moe": (["moe.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),

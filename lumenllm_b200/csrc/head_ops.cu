@@ -14,6 +14,7 @@
 // All arithmetic is float32. A projection arrives as the S partial sums of a split matrix
 // product, [S, rows, width], added in rising order of S wherever a value is read.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 __device__ __forceinline__ float parts_sum(const float* p, int S, size_t stride) {
     float x = p[0];
@@ -178,19 +179,20 @@ LUMEN_API int lumen_latent_store(const float* u, int n_split, long long split_st
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int W, const TW* __restrict__ uk, int H,
-                    int d, int r, int R, const float2* __restrict__ cs, int rot, TO* __restrict__ out, int N) {
+                    int d, int r, int R, const float2* __restrict__ cs, int rot, TO* __restrict__ out, int product,
+                    int N) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float qs[];          // [LQ_TOK][d]
     const int h = blockIdx.y, n0 = blockIdx.x * LQ_TOK, tid = threadIdx.x;
     const int nt = min(LQ_TOK, N - n0);
-    for (int i = tid; i < LQ_TOK * d; i += 128) {
+    if (product) for (int i = tid; i < LQ_TOK * d; i += 128) {
         const int t = i / d, j = i - t * d;
         qs[i] = t < nt ? parts_sum(q + (size_t)(n0 + t) * W + h * (d + r) + j, S, split_stride) : 0.0f;
     }
     __syncthreads();
     const TW* w = uk + (size_t)h * d * R;
-    for (int e = blockIdx.z * 128 + tid; e < R; e += 128 * gridDim.z) {
+    if (product) for (int e = blockIdx.z * 128 + tid; e < R; e += 128 * gridDim.z) {
         float acc[LQ_TOK];
 #pragma unroll
         for (int t = 0; t < LQ_TOK; ++t) acc[t] = 0.0f;
@@ -221,16 +223,17 @@ latent_query_kernel(const float* __restrict__ q, int S, size_t split_stride, int
 
 LUMEN_API int lumen_latent_query(const float* q, int n_split, long long split_stride, int W, const void* uk,
                                  int uk_is_bf16, int H, int d, int r, int R, const float* cs, int rot, void* out,
-                                 int out_is_bf16, int N, cudaStream_t stream) {
+                                 int out_is_bf16, int product, int N, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (H <= 0 || H > 65535 || d <= 0 || r < 0 || R <= 0 || rot < 0 || rot > r || (rot & 1) || W < H * (d + r) ||
         n_split < 1 || (size_t)LQ_TOK * d * sizeof(float) > 48 * 1024)
         return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid((N + LQ_TOK - 1) / LQ_TOK, H, (R + 127) / 128);
+    // product 0: the R numbers of every head are already there (lumen_head_gemm); only the rotated ones are made
+    dim3 grid((N + LQ_TOK - 1) / LQ_TOK, H, product ? (R + 127) / 128 : 1);
     const size_t smem = (size_t)LQ_TOK * d * sizeof(float);
 #define LQ_LAUNCH(TW, TO)                                                                                            \
     lumen_launch(latent_query_kernel<TW, TO>, grid, dim3(128), smem, stream, q, n_split, (size_t)split_stride, W,    \
-                 (const TW*)uk, H, d, r, R, (const float2*)cs, rot, (TO*)out, N)
+                 (const TW*)uk, H, d, r, R, (const float2*)cs, rot, (TO*)out, product, N)
     if (uk_is_bf16 && out_is_bf16) LQ_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (uk_is_bf16) LQ_LAUNCH(__nv_bfloat16, float);
     else if (out_is_bf16) LQ_LAUNCH(float, __nv_bfloat16);
@@ -298,6 +301,156 @@ LUMEN_API int lumen_head_product(const float* x, const void* w, int w_is_bf16, v
     else
         lumen_launch(head_product_kernel<float, float>, grid, dim3(256), smem, stream, x, (const float*)w, (float*)out, N,
                      H, J, E);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- the same products on the tensor cores
+// out[n, h, e] = sum_j x[n, h, j] B_h[j, e] for every head h, with x float32 (possibly partial sums,
+// rounded to bfloat16 as it is staged), B_h bfloat16 and out bfloat16; mma.sync m16n8k16 with
+// float32 accumulation. B_h is stored either [J][E] (B_KN: the keys' up-projection, whose rows are
+// the plain query values) or [E][J] (the values' up-projection). A block takes 64 tokens and 128
+// outputs of one head and walks j 32 at a time; the next step's operands are on their way to
+// registers while this step's are multiplied. Row n of x starts at x + n xrs + h xhs, row n of out
+// at out + n ors + h ohs.
+#define HG_M 64
+#define HG_N 128
+#define HG_K 32
+#define HG_LDA (HG_K + 8)
+#define HG_LDB_KN (HG_N + 8)
+template <bool B_KN>
+__global__ void __launch_bounds__(128)
+head_gemm_kernel(const float* __restrict__ x, int S, size_t split_stride, long long xrs, int xhs,
+                 const __nv_bfloat16* __restrict__ w, int ldw, long long w_head_stride, __nv_bfloat16* __restrict__ out,
+                 long long ors, int ohs, int N, int J, int E) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 As[HG_M * HG_LDA];
+    __shared__ __align__(16) __nv_bfloat16 Bs[B_KN ? HG_K * HG_LDB_KN : HG_N * HG_LDA];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * HG_M, e0 = blockIdx.y * HG_N, h = blockIdx.z;
+    const __nv_bfloat16* wh = w + (size_t)h * w_head_stride;
+
+    // what this thread stages: 16 values of one row of x, and 32 values of one row of B
+    const int ar = tid >> 1, ac = (tid & 1) * 16;
+    const bool a_ok = n0 + ar < N;
+    const float* xa = x + (size_t)(n0 + ar) * xrs + (size_t)h * xhs + ac;
+    float4 pa[4];
+    uint4 pb[4];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            pa[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (a_ok) {
+                pa[i] = *reinterpret_cast<const float4*>(xa + k0 + 4 * i);
+                for (int sp = 1; sp < S; ++sp) {
+                    const float4 v = *reinterpret_cast<const float4*>(xa + (size_t)sp * split_stride + k0 + 4 * i);
+                    pa[i].x += v.x; pa[i].y += v.y; pa[i].z += v.z; pa[i].w += v.w;
+                }
+            }
+        }
+        if (B_KN) {         // row k0 + tid / 4 of B, 32 outputs from e0 + (tid % 4) * 32
+            const int bk = tid >> 2, bc = e0 + (tid & 3) * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                pb[i] = (bc + 8 * i < E) ? *reinterpret_cast<const uint4*>(wh + (size_t)(k0 + bk) * ldw + bc + 8 * i)
+                                         : make_uint4(0u, 0u, 0u, 0u);
+        } else {            // row e0 + tid of B, its 32 values from k0
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                pb[i] = (e0 + tid < E) ? *reinterpret_cast<const uint4*>(wh + (size_t)(e0 + tid) * ldw + k0 + 8 * i)
+                                       : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint2 v;
+            v.x = pack_bf16(pa[i].x, pa[i].y);
+            v.y = pack_bf16(pa[i].z, pa[i].w);
+            *reinterpret_cast<uint2*>(As + ar * HG_LDA + ac + 4 * i) = v;
+        }
+        if (B_KN) {
+            const int bk = tid >> 2, bc = (tid & 3) * 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Bs + bk * HG_LDB_KN + bc + 8 * i) = pb[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(Bs + tid * HG_LDA + 8 * i) = pb[i];
+        }
+    };
+
+    float acc[HG_N / 8][4];
+#pragma unroll
+    for (int i = 0; i < HG_N / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    const uint32_t a_addr = smem_u32(As) + (uint32_t)(((16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * HG_LDA + (lane >> 4) * 8) * 2);
+    const int mi = lane >> 3;
+    const uint32_t b_addr = B_KN ? smem_u32(Bs) + (uint32_t)((((mi & 1) * 8 + (lane & 7)) * HG_LDB_KN + (mi >> 1) * 8) * 2)
+                                 : smem_u32(Bs) + (uint32_t)((((lane & 7)) * HG_LDA + mi * 8) * 2);
+    fetch(0);
+    for (int k0 = 0; k0 < J; k0 += HG_K) {
+        __syncthreads();            // the step before has been multiplied
+        stage();
+        __syncthreads();
+        if (k0 + HG_K < J) fetch(k0 + HG_K);
+        uint32_t a[2][4];
+        ldsm_x4(a[0], a_addr);
+        ldsm_x4(a[1], a_addr + 32);
+        if (B_KN) {
+#pragma unroll
+            for (int np = 0; np < HG_N / 16; ++np)
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    uint32_t r[4];
+                    ldsm_x4_t(r, b_addr + (uint32_t)((16 * kk * HG_LDB_KN + 16 * np) * 2));
+                    mma_bf16(acc[2 * np], a[kk], r[0], r[1]);
+                    mma_bf16(acc[2 * np + 1], a[kk], r[2], r[3]);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < HG_N / 8; ++nt) {
+                uint32_t r[4];
+                ldsm_x4(r, b_addr + (uint32_t)(8 * nt * HG_LDA * 2));
+                mma_bf16(acc[nt], a[0], r[0], r[1]);
+                mma_bf16(acc[nt], a[1], r[2], r[3]);
+            }
+        }
+    }
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = n0 + 16 * warp + g, r1 = r0 + 8;
+#pragma unroll
+    for (int nt = 0; nt < HG_N / 8; ++nt) {
+        const int e = e0 + 8 * nt + 2 * t;
+        if (e < E) {
+            if (r0 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][0], acc[nt][1]);
+            if (r1 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][2], acc[nt][3]);
+        }
+    }
+}
+
+// 1 if lumen_head_gemm takes these sizes: j in steps of 32, rows of x, B and out that keep 16-, 16-
+// and 4-byte alignment.
+LUMEN_API int lumen_head_gemm_takes(long long xrs, int xhs, long long split_stride, int ldw, long long w_head_stride,
+                                    long long ors, int ohs, int J, int E) {
+    return (J > 0 && J % HG_K == 0 && E > 0 && E % 8 == 0 && xrs % 4 == 0 && xhs % 4 == 0 && split_stride % 4 == 0 &&
+            ldw % 8 == 0 && w_head_stride % 8 == 0 && ors % 2 == 0 && ohs % 2 == 0) ? 1 : 0;
+}
+
+// b_kn 1: B_h = w + h w_head_stride is [J][E] with rows ldw apart; 0: [E][J].
+LUMEN_API int lumen_head_gemm(const float* x, int n_split, long long split_stride, long long xrs, int xhs, const void* w,
+                              int b_kn, int ldw, long long w_head_stride, void* out, long long ors, int ohs, int N, int H,
+                              int J, int E, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || H > 65535 || n_split < 1 || (E + HG_N - 1) / HG_N > 65535 ||
+        !lumen_head_gemm_takes(xrs, xhs, split_stride, ldw, w_head_stride, ors, ohs, J, E))
+        return LUMEN_ERR_UNSUPPORTED;
+    dim3 grid((N + HG_M - 1) / HG_M, (E + HG_N - 1) / HG_N, H);
+    if (b_kn)
+        lumen_launch(head_gemm_kernel<true>, grid, dim3(128), 0, stream, x, n_split, (size_t)split_stride, xrs, xhs,
+                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E);
+    else
+        lumen_launch(head_gemm_kernel<false>, grid, dim3(128), 0, stream, x, n_split, (size_t)split_stride, xrs, xhs,
+                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

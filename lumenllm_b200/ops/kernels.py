@@ -795,11 +795,31 @@ def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim, out_dtype=F
         if tuple(cs.shape) != (N, rotary_dim // 2, 2):
             raise KernelError(f"latent_query: angles {tuple(cs.shape)} do not fit {N} tokens and {rotary_dim}")
     out = torch.empty((N, heads, rank + rot_width), dtype=out_dtype, device=q.device)
+    Wo = rank + rot_width
+    product = 1
+    if out_dtype == BF16 and up_k.dtype == BF16 and _head_gemm_takes(W, d + rot_width, N * W, rank, d * rank,
+                                                                   heads * Wo, Wo, d, rank):
+        # the products on the tensor cores; the kernel below then only moves and rotates the rest
+        g = fn("head_ops", "lumen_head_gemm", _HEAD_GEMM_ARGS)
+        check(g(ptr(q), S, N * W, W, d + rot_width, ptr(up_k), 1, rank, d * rank, ptr(out), heads * Wo, Wo, N,
+                int(heads), int(d), int(rank), stream_ptr()), "head_gemm")
+        product = 0
     f = fn("head_ops", "lumen_latent_query",
-           [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, c_int, P])
+           [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, c_int, c_int, P])
     check(f(ptr(q), S, N * W, W, ptr(up_k), _is_bf16(up_k), int(heads), int(d), int(rot_width), int(rank),
-            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(out), _is_bf16(out), N, stream_ptr()), "latent_query")
+            ptr(cs) if rotary_dim else 0, int(rotary_dim), ptr(out), _is_bf16(out), product, N, stream_ptr()),
+          "latent_query")
     return out
+
+
+_HEAD_GEMM_ARGS = [P, c_int, c_longlong, c_longlong, c_int, P, c_int, c_int, c_longlong, P, c_longlong, c_int, c_int,
+                   c_int, c_int, c_int, P]
+
+
+def _head_gemm_takes(xrs, xhs, split_stride, ldw, w_head_stride, ors, ohs, J, E) -> bool:
+    f = int_fn("head_ops", "lumen_head_gemm_takes",
+               [c_longlong, c_int, c_longlong, c_int, c_longlong, c_longlong, c_int, c_int, c_int])
+    return bool(f(int(xrs), int(xhs), int(split_stride), int(ldw), int(w_head_stride), int(ors), int(ohs), int(J), int(E)))
 
 
 ATTN_LATENT_ROWS = 64      # (token, head) rows a block of attn_latent takes
@@ -811,7 +831,7 @@ def attn_latent_takes(width, value_dim, dtype) -> bool:
     with the queries and two key tiles, values that are multiples of 8 up to 512."""
     if dtype != BF16:
         return False
-    f = fn("attn_latent", "lumen_attn_latent_takes", [c_int, c_int])
+    f = int_fn("attn_latent", "lumen_attn_latent_takes", [c_int, c_int])
     return bool(f(int(width), int(value_dim)))
 
 
@@ -847,13 +867,18 @@ def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, windo
 
 def head_product(x, w, out_dtype):
     """out[n, h, :] = w_h x[n, h, :] with w [heads * E, J] cut into `heads` matrices [E, J]; x float32
-    [N, heads, J]; returns [N, heads * E] in out_dtype."""
+    [N, heads, J]; returns [N, heads * E] in out_dtype. In bfloat16, with J a multiple of 32 and E of
+    8, on the tensor cores (x rounded to bfloat16 as it is staged)."""
     require(x, F32, "head_product.x")
     N, H, J = x.shape
     if w.dim() != 2 or w.shape[1] != J or w.shape[0] % H or not w.is_contiguous():
         raise KernelError(f"head_product: weight {tuple(w.shape)} does not fit {H} heads of {J}")
     E = w.shape[0] // H
     out = torch.empty((N, H * E), dtype=out_dtype, device=x.device)
+    if out_dtype == BF16 and w.dtype == BF16 and _head_gemm_takes(H * J, J, 0, J, E * J, H * E, E, J, E):
+        g = fn("head_ops", "lumen_head_gemm", _HEAD_GEMM_ARGS)
+        check(g(ptr(x), 1, 0, H * J, J, ptr(w), 0, J, E * J, ptr(out), H * E, E, N, H, J, E, stream_ptr()), "head_gemm")
+        return out
     f = fn("head_ops", "lumen_head_product", [P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, P])
     check(f(ptr(x), ptr(w), _is_bf16(w), ptr(out), _is_bf16(out), N, H, J, E, stream_ptr()), "head_product")
     return out
@@ -951,12 +976,15 @@ def delta_rule(x, q_col, k_col, v_col, u, beta_col, a, dt_bias, a_log, state, cu
     require(cu_q, I32, "delta_rule.cu_q")
     require(seq_slot, I32, "delta_rule.seq_slot")
     y = torch.empty((N, heads * dv), dtype=F32, device=x.device)
+    # what does not depend on the state, a row a (token, head), made by the kernel's first launch
+    row = int_fn("delta_rule", "lumen_delta_rule_scratch_row", [c_int])(int(d))
+    prep = torch.empty((N, int(heads), row), dtype=F32, device=x.device)
     f = fn("delta_rule", "lumen_delta_rule",
            [P, c_int, c_int, c_int, c_int, P, c_int, c_longlong, c_int, c_int, P, c_int, c_longlong, P, P, P, c_longlong,
-            P, P, c_int, P, c_int, c_int, c_int, c_int, P])
+            P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, P])
     check(f(ptr(x), C, int(q_col), int(k_col), int(v_col), ptr(u), uS, N * u.shape[2], u.shape[2], int(beta_col), ptr(a),
             aS, N * heads * d, ptr(dt_bias), ptr(a_log), ptr(state), state.stride(0), ptr(cu_q), ptr(seq_slot),
-            int(n_seqs), ptr(y), int(heads), int(kv_heads), int(d), int(dv), stream_ptr()), "delta_rule")
+            int(n_seqs), ptr(y), ptr(prep), N, int(heads), int(kv_heads), int(d), int(dv), stream_ptr()), "delta_rule")
     return y
 
 

@@ -715,3 +715,76 @@ def test_trace_replay_writes_the_wanted_logits(models, plain, tmp_path):
     close(read(1), rb[8:9], F32, "the short request's last token")
     for t in range(9):
         close(read(2 + t), ra[31 + t:32 + t], F32, f"decoded {t}")
+
+
+# ------------------------------------------------------------------ the tensor-core kernels of latent attention alone
+def _latent_case(lens, starts, H, W, seed, n_pages=24):
+    """A latent cache [pages, 1, 64, W] that holds starts[b] + lens[b] rows a sequence on pages that
+    are not in order, and queries [sum lens, H, W] for every sequence's last lens[b] positions."""
+    g = torch.Generator().manual_seed(seed)
+    totals = [s + n for s, n in zip(starts, lens)]
+    table = torch.zeros(len(lens), max((t + 63) // 64 for t in totals), dtype=torch.int32)
+    free = list(range(n_pages - 1, 0, -1))
+    cache = torch.zeros(n_pages, 1, 64, W)
+    rows = []
+    for b, t in enumerate(totals):
+        r = torch.randn(t, W, generator=g).to(BF16).float()
+        rows.append(r)
+        for p in range((t + 63) // 64):
+            pg = free.pop(2 if len(free) > 2 else 0)
+            table[b, p] = pg
+            n = min(64, t - 64 * p)
+            cache[pg, 0, :n] = r[64 * p:64 * p + n]
+    q = [(0.3 * torch.randn(n, H, W, generator=g)).to(BF16).float() for n in lens]
+    return table, cache, rows, q
+
+
+@pytest.mark.parametrize("H,W,dv,window", [(3, 64, 48, 0), (16, 176, 160, 45), (70, 64, 40, 33), (4, 352, 320, 100),
+                                           (2, 96, 96, 1), (1, 32, 8, 64)])
+def test_latent_attention_kernel_against_plain_sums(H, W, dv, window):
+    """Prompts, a prompt's later portion and single tokens in one launch: (token, head) rows that
+    straddle tokens, more heads than a block has rows, windows that end inside a tile of keys, value
+    widths that fill one, two and four warps' columns."""
+    from lumenllm_b200.ops import kernels as K
+    lens, starts = [70, 1, 1, 130], [0, 299, 63, 5]
+    table, cache, rows, q = _latent_case(lens, starts, H, W, seed=31)
+    assert K.attn_latent_takes(W, dv, BF16)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    scale = 0.2
+    for q_lens in (lens, None):          # None: a captured step, the division of the tokens is read on the device
+        got = K.attn_latent(torch.cat(q).to(BF16).cuda(), cache.to(BF16).cuda(), table.cuda(), cu.cuda(),
+                            torch.tensor(starts, dtype=torch.int32).cuda(), q_lens, dv, window, scale,
+                            n_seqs=len(lens)).cpu()
+        ref = []
+        for b, (n, s) in enumerate(zip(lens, starts)):
+            pos = torch.arange(s, s + n)[:, None]
+            j = torch.arange(s + n)[None, :]
+            seen = (j <= pos) & ((pos - j < window) if window else torch.ones_like(j, dtype=torch.bool))
+            sc = torch.einsum("nhw,tw->nht", q[b], rows[b]) * scale
+            sc = sc.masked_fill(~seen[:, None, :], float("-inf"))
+            ref.append(torch.einsum("nht,tv->nhv", torch.softmax(sc, dim=-1), rows[b][:, :dv]))
+        ref = torch.cat(ref)
+        assert got.shape == ref.shape and torch.isfinite(got).all()
+        assert float((got - ref).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("N", [1, 9, 150])
+def test_products_of_every_head_on_the_tensor_cores(N):
+    """Both per-head products of latent attention against float32 sums: the query into the latent
+    space from partial sums (outputs that do not fill a block's 128 columns), and the weighted sums
+    back through the values' up-projection."""
+    from lumenllm_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(41)
+    H, d, r, R, dv = 3, 64, 16, 200, 40
+    qf = torch.randn(N, H * (d + r), generator=g)
+    uk = (0.2 * torch.randn(H * d, R, generator=g)).to(BF16)
+    parts = torch.stack([0.5 * qf, 0.125 * qf, 0.375 * qf]).cuda()
+    got = K.latent_query(parts, uk.cuda(), H, d, r, R, None, 0, out_dtype=BF16).float().cpu()
+    qh = qf.view(N, H, d + r)
+    ref = torch.cat([torch.einsum("nhj,hjr->nhr", qh[:, :, :d].to(BF16).float(), uk.float().view(H, d, R)), qh[:, :, d:]], dim=-1)
+    assert float((got - ref).abs().max()) < 3e-2 * max(1.0, float(ref.abs().max()))
+    x = torch.randn(N, H, R + 24, generator=g)         # J = 224
+    uv = (0.2 * torch.randn(H * dv, R + 24, generator=g)).to(BF16)
+    got = K.head_product(x.cuda(), uv.cuda(), BF16).float().cpu()
+    ref = torch.einsum("nhj,hej->nhe", x.to(BF16).float(), uv.float().view(H, dv, R + 24)).reshape(N, H * dv)
+    assert float((got - ref).abs().max()) < 3e-2 * max(1.0, float(ref.abs().max()))
