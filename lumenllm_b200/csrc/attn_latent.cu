@@ -32,8 +32,8 @@ template <int DVS>
 __global__ void __launch_bounds__(AL_THREADS)
 attn_latent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
-                   const int* __restrict__ seq_start, int B, float* __restrict__ out, int H, int W, int dv,
-                   int window, float scale_log2, int* __restrict__ err) {
+                   const int* __restrict__ seq_start, int B, float* __restrict__ out, float* __restrict__ part,
+                   size_t rows_total, int H, int W, int dv, int window, float scale_log2, int* __restrict__ err) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem[];
@@ -80,7 +80,7 @@ attn_latent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         __syncwarp();
         bulk_load(ks + ((size_t)stage * AL_KEYS + lane) * WP, src + (size_t)lane * W, row_bytes, &full[stage]);
     };
-    if (warp == 0) issue(0, kt_lo);
+    if (warp == 0 && kt_lo + (int)blockIdx.y <= kt_hi) issue(0, kt_lo + blockIdx.y);
 
     // the tile's query rows, 16 bytes at a time; rows past the sequence's last are zeros
     {
@@ -111,9 +111,10 @@ attn_latent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const uint32_t qs_a = smem_u32(qs) + (uint32_t)(((16 * rg + (lane & 7) + ((lane >> 3) & 1) * 8) * WP + (lane >> 4) * 8) * 2);
     const int ksteps = W / 16;
 
-    for (int kt = kt_lo, it = 0; kt <= kt_hi; ++kt, ++it) {
+    const int n_split = gridDim.y, sp = blockIdx.y;     // block sp walks every n_split-th tile of keys
+    for (int kt = kt_lo + sp, it = 0; kt <= kt_hi; kt += n_split, ++it) {
         const int stage = it & 1;
-        if (warp == 0 && kt + 1 <= kt_hi) issue(stage ^ 1, kt + 1);
+        if (warp == 0 && kt + n_split <= kt_hi) issue(stage ^ 1, kt + n_split);
         if (!mbar_wait(&full[stage], (it >> 1) & 1)) failed = true;
         const uint32_t kbase = smem_u32(ks + (size_t)stage * AL_KEYS * WP);
 
@@ -214,6 +215,24 @@ attn_latent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
 
     if (!active) return;
+    if (n_split > 1) {
+        // this block's share, not normed: [o (dv) | running maximum (log2 units), running sum] a row
+        float* p0r = part + ((size_t)sp * rows_total + grow0 + r0) * (dv + 2);
+        float* p1r = part + ((size_t)sp * rows_total + grow0 + r1) * (dv + 2);
+#pragma unroll
+        for (int nt = 0; nt < DVS / 8; ++nt) {
+            const int col = c * DVS + 8 * nt + 2 * t;
+            if (col < dv) {
+                if (r0 < nrows) *reinterpret_cast<float2*>(p0r + col) = make_float2(o[nt][0], o[nt][1]);
+                if (r1 < nrows) *reinterpret_cast<float2*>(p1r + col) = make_float2(o[nt][2], o[nt][3]);
+            }
+        }
+        if (c == 0 && t == 0) {
+            if (r0 < nrows) *reinterpret_cast<float2*>(p0r + dv) = make_float2(m0, l0);
+            if (r1 < nrows) *reinterpret_cast<float2*>(p1r + dv) = make_float2(m1, l1);
+        }
+        return;
+    }
     const float inv0 = (l0 > 0.0f) ? 1.0f / l0 : 0.0f, inv1 = (l1 > 0.0f) ? 1.0f / l1 : 0.0f;
     float* o0 = out + (grow0 + r0) * dv;
     float* o1 = out + (grow0 + r1) * dv;
@@ -224,6 +243,31 @@ attn_latent_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             if (r0 < nrows) *reinterpret_cast<float2*>(o0 + col) = make_float2(o[nt][0] * inv0, o[nt][1] * inv0);
             if (r1 < nrows) *reinterpret_cast<float2*>(o1 + col) = make_float2(o[nt][2] * inv1, o[nt][3] * inv1);
         }
+    }
+}
+
+// The shares of a row's n_split blocks become the row: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s,
+// always in the order of s. A block a row.
+#define AL_MAX_SPLIT 16
+__global__ void __launch_bounds__(128)
+attn_latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, size_t rows_total, int dv, int n_split) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t row = blockIdx.x;
+    float w[AL_MAX_SPLIT];
+    float M = -INFINITY, L = 0.0f;
+    for (int s = 0; s < n_split; ++s) M = fmaxf(M, part[((size_t)s * rows_total + row) * (dv + 2) + dv]);
+    for (int s = 0; s < n_split; ++s) {
+        const float* p = part + ((size_t)s * rows_total + row) * (dv + 2) + dv;
+        w[s] = (p[0] == -INFINITY) ? 0.0f : exp2f(p[0] - M);
+        L += w[s] * p[1];
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int e = threadIdx.x; e < dv; e += 128) {
+        float acc = 0.0f;
+        for (int s = 0; s < n_split; ++s)
+            if (w[s] != 0.0f) acc = fmaf(w[s], part[((size_t)s * rows_total + row) * (dv + 2) + e], acc);
+        out[row * dv + e] = acc * inv;
     }
 }
 
@@ -241,11 +285,18 @@ LUMEN_API int lumen_attn_latent_takes(int W, int dv) {
 // q bfloat16 [N, H, W]; cache bfloat16 [pages, 1, PAGE, W] (plain tiles); out float32 [N, H, dv];
 // cu_q int32 [B+1]; seq_start int32 [B] (cached length of each sequence before this step);
 // n_tiles >= the sum over sequences of ceil(q_len H / 64) (blocks left over return at once).
+// n_split > 1 (steps of few rows, as decode steps are): a row's keys are shared out among n_split
+// blocks, tile by tile in turn, and merged by a second kernel; part then holds
+// n_split * N * H * (dv + 2) floats of scratch. How a row's keys are shared out depends on n_split and
+// the row's own position alone.
 LUMEN_API int lumen_attn_latent(const void* q, const void* cache, const int* block_table, int bt_stride,
-                                const int* cu_q, const int* seq_start, int B, int n_tiles, void* out, int H, int W,
-                                int dv, int window, float scale, int* err, cudaStream_t stream) {
-    if (B <= 0 || n_tiles <= 0) return 0;
+                                const int* cu_q, const int* seq_start, int B, int n_tiles, void* out, void* part,
+                                int n_split, int N, int H, int W, int dv, int window, float scale, int* err,
+                                cudaStream_t stream) {
+    if (B <= 0 || n_tiles <= 0 || N <= 0) return 0;
     if (H <= 0 || window < 0 || !lumen_attn_latent_takes(W, dv)) return LUMEN_ERR_UNSUPPORTED;
+    if (n_split < 1 || n_split > AL_MAX_SPLIT || (n_split > 1 && !part)) return LUMEN_ERR_BAD_ARGUMENT;
+    const size_t rows_total = (size_t)N * H;
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = attn_latent_smem(W);
     const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
@@ -255,13 +306,20 @@ LUMEN_API int lumen_attn_latent(const void* q, const void* cache, const int* blo
         auto k = attn_latent_kernel<S>;                                                                           \
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
         if (e != cudaSuccess) return (int)e;                                                                      \
-        lumen_launch(k, dim3(n_tiles), dim3(AL_THREADS), smem, stream, qp, cp, block_table, bt_stride, cu_q,      \
-                     seq_start, B, (float*)out, H, W, dv, window, scale_log2, err);                               \
+        lumen_launch(k, dim3(n_tiles, n_split), dim3(AL_THREADS), smem, stream, qp, cp, block_table, bt_stride,   \
+                     cu_q, seq_start, B, (float*)out, (float*)part, rows_total, H, W, dv, window, scale_log2,     \
+                     err);                                                                                        \
     } while (0)
     if (dv <= 128) AL_LAUNCH(32);
     else if (dv <= 256) AL_LAUNCH(64);
     else AL_LAUNCH(128);
 #undef AL_LAUNCH
     LUMEN_LAUNCH_CHECK();
+    if (n_split > 1) {
+        if (rows_total > 0x7fffffffu) return LUMEN_ERR_UNSUPPORTED;
+        lumen_launch(attn_latent_merge_kernel, dim3((unsigned)rows_total), dim3(128), 0, stream, (const float*)part,
+                     (float*)out, rows_total, dv, n_split);
+        LUMEN_LAUNCH_CHECK();
+    }
     return 0;
 }

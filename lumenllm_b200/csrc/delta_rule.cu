@@ -87,16 +87,19 @@ delta_prepare_kernel(const float* __restrict__ x, int C, int q_col, int k_col,
     }
 }
 
+// NS: threads that share a column of S (a power of two, NS DR_ROWS >= d); every offset of the walk is
+// a constant of the instance.
+template <int NS>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __restrict__ prep,
                   float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
-                  const int* __restrict__ seq_slot, float* __restrict__ y, int H, int d, int dv, int NS) {
+                  const int* __restrict__ seq_slot, float* __restrict__ y, int H, int d, int dv) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    const int dp = NS * DR_ROWS;                    // d padded to what the threads of a column hold
-    const int PW = 3 * dp + 4;
-    const int cols = DR_THREADS / NS;
+    constexpr int dp = NS * DR_ROWS;                // d padded to what the threads of a column hold
+    constexpr int PW = 3 * dp + 4;
+    constexpr int cols = DR_THREADS / NS;
     float* rows = sm;                               // [2][DR_CHUNK][PW]
     float* vs = sm + 2 * DR_CHUNK * PW;             // [2][DR_CHUNK][cols]
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -116,7 +119,7 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
 
     auto issue = [&](int t0, int buf) {
         const int nt = min(DR_CHUNK, t_end - t0);
-        const int pieces = PW / 4;
+        constexpr int pieces = PW / 4;
         float* rb = rows + buf * DR_CHUNK * PW;
         for (int i = tid; i < nt * pieces; i += DR_THREADS) {
             const int tt = i / pieces, p = i - tt * pieces;
@@ -143,6 +146,7 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
         __syncthreads();
         const float* rb = rows + buf * DR_CHUNK * PW;
         const float* vb = vs + buf * DR_CHUNK * cols;
+#pragma unroll 2
         for (int t = 0; t < nt; ++t) {
             const float* qn = rb + t * PW;
             const float* kn = qn + dp;
@@ -162,6 +166,7 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
                 w = fmaf(S[i * 4 + 0], q4.x, w); w = fmaf(S[i * 4 + 1], q4.y, w);
                 w = fmaf(S[i * 4 + 2], q4.z, w); w = fmaf(S[i * 4 + 3], q4.w, w);
             }
+#pragma unroll
             for (int o = NS >> 1; o > 0; o >>= 1) {
                 r += __shfl_xor_sync(0xffffffffu, r, o);
                 w += __shfl_xor_sync(0xffffffffu, w, o);
@@ -221,12 +226,25 @@ LUMEN_API int lumen_delta_rule(const float* x, int C, int q_col, int k_col, int 
     dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
     if (grid.z > 65535) return LUMEN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)2 * DR_CHUNK * (3 * dp + 4 + cols) * sizeof(float);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+#define DR_LAUNCH(S)                                                                                                  \
+    do {                                                                                                              \
+        auto k = delta_rule_kernel<S>;                                                                                \
+        if (smem > 48 * 1024) {                                                                                       \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (e != cudaSuccess) return (int)e;                                                                      \
+        }                                                                                                             \
+        lumen_launch(k, grid, dim3(DR_THREADS), smem, stream, x, C, v_col, (const float*)prep, state,                 \
+                     (size_t)slot_stride, cu_q, seq_slot, y, H, d, dv);                                               \
+    } while (0)
+    switch (NS) {
+        case 1: DR_LAUNCH(1); break;
+        case 2: DR_LAUNCH(2); break;
+        case 4: DR_LAUNCH(4); break;
+        case 8: DR_LAUNCH(8); break;
+        case 16: DR_LAUNCH(16); break;
+        default: DR_LAUNCH(32); break;
     }
-    lumen_launch(delta_rule_kernel, grid, dim3(DR_THREADS), smem, stream, x, C, v_col, (const float*)prep, state,
-                 (size_t)slot_stride, cu_q, seq_slot, y, H, d, dv, NS);
+#undef DR_LAUNCH
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

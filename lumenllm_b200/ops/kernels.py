@@ -835,13 +835,17 @@ def attn_latent_takes(width, value_dim, dtype) -> bool:
     return bool(f(int(width), int(value_dim)))
 
 
-def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, window, scale, n_seqs=None):
+ATTN_LATENT_DECODE_SPLIT = 8   # blocks that share a row's keys in steps of one token a sequence
+
+
+def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, window, scale, n_seqs=None, n_split=1):
     """Causal attention over a latent cache on the tensor cores (mma.sync): q bfloat16 [N, H, W],
     already in the cache's space; cache bfloat16 [pages, 1, PAGE, W] (plain tiles), a row the key of
     every head and its first value_dim numbers the value of every head; a query at position p sees
     key j if 0 <= p - j < window (window 0: every earlier key). Returns float32 [N, H, value_dim].
     Prompts and decoded tokens alike; q_lens (host list) or, with q_lens None, n_seqs = B as in
-    attn_prefill."""
+    attn_prefill. n_split > 1 shares a row's keys out among that many blocks (a second kernel merges
+    them): for steps with few rows."""
     N, H, W = q.shape
     B = len(q_lens) if q_lens is not None else int(n_seqs)
     require(q, BF16, "attn_latent.q")
@@ -857,11 +861,13 @@ def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, windo
     # sum of ceil(q_b H / rows) over any division of N tokens into B sequences is at most N H // rows + B
     n_tiles = sum((n * H + rows - 1) // rows for n in q_lens) if q_lens is not None else N * H // rows + B
     out = torch.empty((N, H, int(value_dim)), dtype=F32, device=q.device)
+    n_split = int(n_split)
+    part = torch.empty((n_split, N * H, int(value_dim) + 2), dtype=F32, device=q.device) if n_split > 1 else None
     f = fn("attn_latent", "lumen_attn_latent",
-           [P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P, P])
+           [P, P, P, c_int, P, P, c_int, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P])
     check(f(ptr(q), ptr(cache), ptr(block_table), block_table.stride(0), ptr(cu_q), ptr(seq_start), B, n_tiles,
-            ptr(out), H, W, int(value_dim), int(window), float(scale), ptr(error_flag(q.device)), stream_ptr()),
-          "attn_latent")
+            ptr(out), ptr(part), n_split, N, H, W, int(value_dim), int(window), float(scale),
+            ptr(error_flag(q.device)), stream_ptr()), "attn_latent")
     return out
 
 

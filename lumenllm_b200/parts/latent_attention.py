@@ -101,7 +101,7 @@ class LatentAttention:
             # a captured step is replayed for other divisions of its tokens than the one it was captured with
             q_lens = None if ctx.extras.get("captured") else ctx.q_lens
             mixed = K.attn_latent(q, kc, table, ctx.cu_q, ctx.seq_start, q_lens, self.R, self.window, self.scale,
-                                  n_seqs=ctx.B)
+                                  n_seqs=ctx.B, n_split=K.ATTN_LATENT_DECODE_SPLIT if ctx.is_decode else 1)
         else:
             q = K.latent_query(u, self.uk, self.H, self.d, self.r, self.R, cs, rot)
             mixed = K.attn_generic_opt(q, kc, None, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,

@@ -751,10 +751,12 @@ def test_latent_attention_kernel_against_plain_sums(H, W, dv, window):
     assert K.attn_latent_takes(W, dv, BF16)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
     scale = 0.2
-    for q_lens in (lens, None):          # None: a captured step, the division of the tokens is read on the device
+    # None: a captured step, the division of the tokens is read on the device; 8 and 3: a row's keys shared
+    # out among blocks (more of them than some rows have tiles of keys)
+    for q_lens, n_split in ((lens, 1), (None, 1), (lens, 8), (None, 3)):
         got = K.attn_latent(torch.cat(q).to(BF16).cuda(), cache.to(BF16).cuda(), table.cuda(), cu.cuda(),
                             torch.tensor(starts, dtype=torch.int32).cuda(), q_lens, dv, window, scale,
-                            n_seqs=len(lens)).cpu()
+                            n_seqs=len(lens), n_split=n_split).cpu()
         ref = []
         for b, (n, s) in enumerate(zip(lens, starts)):
             pos = torch.arange(s, s + n)[:, None]
