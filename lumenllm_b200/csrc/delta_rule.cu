@@ -20,7 +20,7 @@
 #include "common.cuh"
 
 #define DR_THREADS 256
-#define DR_ROWS 16          // rows of S a thread keeps: 4 groups of 4 consecutive rows
+#define DR_ROWS 8           // rows of S a thread keeps (2 groups of 4 consecutive rows), 16 for heads wider than 256
 #define DR_CHUNK 8
 #define DR_PREP_WARPS 4
 
@@ -87,9 +87,10 @@ delta_prepare_kernel(const float* __restrict__ x, int C, int q_col, int k_col,
     }
 }
 
-// NS: threads that share a column of S (a power of two, NS DR_ROWS >= d); every offset of the walk is
-// a constant of the instance.
-template <int NS>
+// NS: threads that share a column of S (a power of two), ROWS: rows of it a thread keeps, NS ROWS >= d;
+// every offset of the walk is a constant of the instance. Eight rows a thread (16 threads a column at
+// 128 key channels) halves a token's chain of sums and doubles the blocks of a head.
+template <int NS, int ROWS>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __restrict__ prep,
                   float* __restrict__ state, size_t slot_stride, const int* __restrict__ cu_q,
@@ -97,7 +98,8 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int dp = NS * DR_ROWS;                // d padded to what the threads of a column hold
+    constexpr int dp = NS * ROWS;                   // d padded to what the threads of a column hold
+    constexpr int GR = ROWS / 4;
     constexpr int PW = 3 * dp + 4;
     constexpr int cols = DR_THREADS / NS;
     float* rows = sm;                               // [2][DR_CHUNK][PW]
@@ -108,9 +110,9 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
     const int s = tid % NS, cj = tid / NS, j = blockIdx.z * cols + cj;
     const bool live = j < dv;
     float* Sj = state + (size_t)seq_slot[b] * slot_stride + ((size_t)h * dv + (live ? j : 0)) * d;
-    float S[DR_ROWS];
+    float S[ROWS];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < GR; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int row = (i * NS + s) * 4 + c;
@@ -152,10 +154,10 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
             const float* kn = qn + dp;
             const float* gd = kn + dp;
             const float vj = vb[t * cols + cj];
-            float rp[4], wp[4];                     // a sum a group of four rows: four short chains, not one of 16
-            float4 k4[4];
+            float rp[GR], wp[GR];                   // a sum a group of four rows: short chains, not one long one
+            float4 k4[GR];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < GR; ++i) {
                 const int off = (i * NS + s) * 4;
                 const float4 g4 = *reinterpret_cast<const float4*>(gd + off);
                 const float4 q4 = *reinterpret_cast<const float4*>(qn + off);
@@ -166,7 +168,11 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
                 wp[i] = S[i * 4 + 0] * q4.x; wp[i] = fmaf(S[i * 4 + 1], q4.y, wp[i]);
                 wp[i] = fmaf(S[i * 4 + 2], q4.z, wp[i]); wp[i] = fmaf(S[i * 4 + 3], q4.w, wp[i]);
             }
-            float r = (rp[0] + rp[1]) + (rp[2] + rp[3]), w = (wp[0] + wp[1]) + (wp[2] + wp[3]);
+            float r = rp[0] + rp[1], w = wp[0] + wp[1];
+            if (GR == 4) {
+                r += rp[GR - 2] + rp[GR - 1];
+                w += wp[GR - 2] + wp[GR - 1];
+            }
 #pragma unroll
             for (int o = NS >> 1; o > 0; o >>= 1) {
                 r += __shfl_xor_sync(0xffffffffu, r, o);
@@ -174,7 +180,7 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
             }
             const float uj = gd[dp + 1] * (vj - r);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < GR; ++i) {
                 S[i * 4 + 0] = fmaf(k4[i].x, uj, S[i * 4 + 0]); S[i * 4 + 1] = fmaf(k4[i].y, uj, S[i * 4 + 1]);
                 S[i * 4 + 2] = fmaf(k4[i].z, uj, S[i * 4 + 2]); S[i * 4 + 3] = fmaf(k4[i].w, uj, S[i * 4 + 3]);
             }
@@ -184,7 +190,7 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < GR; ++i)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int row = (i * NS + s) * 4 + c;
@@ -193,11 +199,19 @@ delta_rule_kernel(const float* __restrict__ x, int C, int v_col, const float* __
     }
 }
 
+// Threads a column and rows a thread for d key channels: 8 rows up to d = 256, 16 beyond.
+static inline void delta_rule_shape(int d, int* ns, int* rows) {
+    *rows = d <= 32 * DR_ROWS ? DR_ROWS : 2 * DR_ROWS;
+    int NS = 1;
+    while (NS * *rows < d) NS <<= 1;
+    *ns = NS;
+}
+
 // Floats of scratch lumen_delta_rule needs for every (token, head) with d key channels.
 LUMEN_API int lumen_delta_rule_scratch_row(int d) {
-    int NS = 1;
-    while (NS * DR_ROWS < d) NS <<= 1;
-    return 3 * NS * DR_ROWS + 4;
+    int NS, rows;
+    delta_rule_shape(d, &NS, &rows);
+    return 3 * NS * rows + 4;
 }
 
 // x float32 [N, C]: the convolved and activated q (G heads of d, from column q_col), k (k_col)
@@ -211,14 +225,14 @@ LUMEN_API int lumen_delta_rule(const float* x, int C, int q_col, int k_col, int 
                                const int* cu_q, const int* seq_slot, int n_seqs, float* y, float* prep, int N, int H,
                                int G, int d, int dv, cudaStream_t stream) {
     if (n_seqs <= 0 || N <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || d > 32 * DR_ROWS || uS < 1 || aS < 1 || H > 65535)
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || d > 64 * DR_ROWS || uS < 1 || aS < 1 || H > 65535)
         return LUMEN_ERR_UNSUPPORTED;
     if (q_col < 0 || k_col < 0 || v_col < 0 || q_col + G * d > C || k_col + G * d > C || v_col + H * dv > C ||
         b_col < 0 || b_col + H > uW || !prep)
         return LUMEN_ERR_BAD_ARGUMENT;
-    int NS = 1;
-    while (NS * DR_ROWS < d) NS <<= 1;
-    const int cols = DR_THREADS / NS, dp = NS * DR_ROWS;
+    int NS, rows;
+    delta_rule_shape(d, &NS, &rows);
+    const int cols = DR_THREADS / NS, dp = NS * rows;
     dim3 pgrid(N, (H + DR_PREP_WARPS - 1) / DR_PREP_WARPS);
     if (pgrid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
     lumen_launch(delta_prepare_kernel, pgrid, dim3(32 * DR_PREP_WARPS), 0, stream, x, C, q_col, k_col, u, uS,
@@ -227,9 +241,9 @@ LUMEN_API int lumen_delta_rule(const float* x, int C, int q_col, int k_col, int 
     dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
     if (grid.z > 65535) return LUMEN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)2 * DR_CHUNK * (3 * dp + 4 + cols) * sizeof(float);
-#define DR_LAUNCH(S)                                                                                                  \
+#define DR_LAUNCH(S, R)                                                                                               \
     do {                                                                                                              \
-        auto k = delta_rule_kernel<S>;                                                                                \
+        auto k = delta_rule_kernel<S, R>;                                                                              \
         if (smem > 48 * 1024) {                                                                                       \
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
             if (e != cudaSuccess) return (int)e;                                                                      \
@@ -237,13 +251,14 @@ LUMEN_API int lumen_delta_rule(const float* x, int C, int q_col, int k_col, int 
         lumen_launch(k, grid, dim3(DR_THREADS), smem, stream, x, C, v_col, (const float*)prep, state,                 \
                      (size_t)slot_stride, cu_q, seq_slot, y, H, d, dv);                                               \
     } while (0)
-    switch (NS) {
-        case 1: DR_LAUNCH(1); break;
-        case 2: DR_LAUNCH(2); break;
-        case 4: DR_LAUNCH(4); break;
-        case 8: DR_LAUNCH(8); break;
-        case 16: DR_LAUNCH(16); break;
-        default: DR_LAUNCH(32); break;
+    if (rows != DR_ROWS) DR_LAUNCH(32, 2 * DR_ROWS);
+    else switch (NS) {
+        case 1: DR_LAUNCH(1, DR_ROWS); break;
+        case 2: DR_LAUNCH(2, DR_ROWS); break;
+        case 4: DR_LAUNCH(4, DR_ROWS); break;
+        case 8: DR_LAUNCH(8, DR_ROWS); break;
+        case 16: DR_LAUNCH(16, DR_ROWS); break;
+        default: DR_LAUNCH(32, DR_ROWS); break;
     }
 #undef DR_LAUNCH
     LUMEN_LAUNCH_CHECK();

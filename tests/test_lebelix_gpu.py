@@ -355,7 +355,9 @@ DELTAS = [delta(2, 1, 24, 16, 3, 5, 3),
           delta(4, 2, 64, 32, 4, 12, 8),
           delta(1, 1, 128, 128, 2, 4, 4),
           delta(6, 2, 16, 8, 4, 2, 1),
-          delta(2, 2, 40, 24, 3, 7, 9)]
+          delta(2, 2, 40, 24, 3, 7, 9),
+          delta(2, 1, 6, 9, 2, 3, 2),              # a column of the state in one thread
+          delta(1, 1, 272, 12, 2, 4, 4)]           # key channels beyond 256: sixteen rows a thread
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
