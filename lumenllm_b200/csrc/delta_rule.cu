@@ -46,7 +46,9 @@ delta_prepare_kernel(const float* __restrict__ x, int C, int q_col, int k_col,
                      const float* __restrict__ u, int uS, size_t u_stride, int uW, int b_col,
                      const float* __restrict__ a, int aS, size_t a_stride, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, float* __restrict__ prep, int N, int H, int G, int d, int dp) {
-    pdl_trigger();
+    // No early trigger here: the walk that follows has about one block an SM and must find the SMs
+    // empty, so that its blocks are spread one an SM; started under this kernel's blocks they were
+    // packed several an SM wherever room was, and the walk took twice as long.
     pdl_wait();
     const int n = blockIdx.x, h = blockIdx.y * DR_PREP_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (h >= H) return;
