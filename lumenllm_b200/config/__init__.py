@@ -5,8 +5,9 @@ from .qwen3 import Qwen3Config
 from .dabevik import DabevikConfig
 from .rasezen import RasezenConfig
 from .lebelix import LebelixConfig
+from .vekolix import VekolixConfig
 from .params import ParametersFile, SamplingDefaults
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig", "RasezenConfig", "LebelixConfig",
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "DabevikConfig", "RasezenConfig", "LebelixConfig", "VekolixConfig",
            "config_class_for", "config_from_dict", "known_architectures", "load_config",
            "register_architecture", "ParametersFile", "SamplingDefaults"]

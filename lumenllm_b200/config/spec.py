@@ -31,13 +31,15 @@ class LayerSpec:
     its own, so one model can mix kinds. `ffn` is None for a layer without a feed-forward
     (where the block arrangement allows that); `extras` holds further parts that an
     arrangement puts around its sublayers (a convolution of a sublayer's input, say), by the
-    names the arrangement gives them."""
+    names the arrangement gives them; `params` holds the arrangement's own constants (a
+    multiplier on every update of the stream, say)."""
     block: str
     mixer: PartSpec
     ffn: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     prefix: str = ""
     extras: Dict[str, PartSpec] = field(default_factory=dict)
+    params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -36,6 +36,7 @@ MODULES = {
     "ssm": (["ssm.cu"], ["common.cuh"]),
     "head_ops": (["head_ops.cu"], ["common.cuh", "mma_utils.cuh"]),
     "delta_rule": (["delta_rule.cu"], ["common.cuh"]),
+    "linear_attn": (["linear_attn.cu"], ["common.cuh"]),
     "moe": (["moe.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "qk_head.cuh", "attn_decode_noalloc.h"]),

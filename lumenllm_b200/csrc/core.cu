@@ -465,10 +465,11 @@ LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf
 }
 
 // ---------------------------------------------------------------- rotation angles
-// cs[n, i] = (cos, sin) of angle = float(pos[n]) * inv_freq[i], i < half. Made once per step
-// and read by every layer that shares the position encoding.
+// cs[n, i] = mag * (cos, sin) of angle = float(pos[n]) * inv_freq[i], i < half. Made once per step
+// and read by every layer that shares the position encoding. mag is 1 unless the encoding
+// stretches its frequencies and makes up for it in the length of the rotated vectors.
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ cs, int N, int half) {
+                                  float2* __restrict__ cs, int N, int half, float mag) {
     pdl_trigger();
     pdl_wait();      // nothing of this kernel touches global memory before this
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -477,14 +478,14 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __re
     const float ang = (float)pos[n] * inv_freq[i];
     float s, c;
     sincosf(ang, &s, &c);
-    cs[idx] = make_float2(c, s);
+    cs[idx] = make_float2(c * mag, s * mag);
 }
 
-LUMEN_API int lumen_rope_table(const int* pos, const float* inv_freq, float* cs, int N, int half,
+LUMEN_API int lumen_rope_table(const int* pos, const float* inv_freq, float* cs, int N, int half, float mag,
                                cudaStream_t stream) {
     if (N <= 0 || half <= 0) return 0;
     const long long total = (long long)N * half;
-    lumen_launch(rope_table_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, pos, inv_freq, (float2*)cs, N, half);
+    lumen_launch(rope_table_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, pos, inv_freq, (float2*)cs, N, half, mag);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -243,6 +243,18 @@ LUMEN_API int lumen_latent_query(const float* q, int n_split, long long split_st
     return 0;
 }
 
+// An optional gate of one number a (token, head): the head's output is multiplied by
+// sigmoid(gate[n, g0 + h]), gate float32 [S, N, W] partial sums; p null: no gate.
+struct HeadGate {
+    const float* p;
+    int S;
+    size_t split_stride;
+    int W, g0;
+    __device__ __forceinline__ float of(int n, int h) const {
+        return p ? sigmoid_f(parts_sum(p + (size_t)n * W + g0 + h, S, split_stride)) : 1.0f;
+    }
+};
+
 // ---------------------------------------------------------------- a product of its own for every head
 // out[n, h, e] = sum_j x[n, h, j] w[h E + e, j]: x float32 [N, H, J], w [H E, J], out [N, H E] in
 // the run's type. A block takes HP_TOK tokens of one head and every gridDim.z-th run of 8 output
@@ -251,7 +263,7 @@ LUMEN_API int lumen_latent_query(const float* q, int n_split, long long split_st
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 head_product_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out, int N, int H, int J,
-                    int E) {
+                    int E, HeadGate hg) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float xs[];          // [HP_TOK][J]
@@ -276,13 +288,16 @@ head_product_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* _
 #pragma unroll
         for (int t = 0; t < HP_TOK; ++t) acc[t] = warp_sum(acc[t]);
         if (lane == 0)
-            for (int t = 0; t < nt; ++t) out[(size_t)(n0 + t) * H * E + h * E + e] = from_f32<TO>(acc[t]);
+            for (int t = 0; t < nt; ++t) out[(size_t)(n0 + t) * H * E + h * E + e] = from_f32<TO>(acc[t] * hg.of(n0 + t, h));
     }
 }
 
 LUMEN_API int lumen_head_product(const float* x, const void* w, int w_is_bf16, void* out, int out_is_bf16, int N, int H,
-                                 int J, int E, cudaStream_t stream) {
+                                 int J, int E, const float* gate, int gate_split, long long gate_split_stride,
+                                 int gate_w, int gate_col, cudaStream_t stream) {
     if (N <= 0) return 0;
+    if (gate && (gate_split < 1 || gate_col < 0 || gate_col + H > gate_w)) return LUMEN_ERR_BAD_ARGUMENT;
+    const HeadGate hg = {gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col};
     if (H <= 0 || H > 65535 || J <= 0 || E <= 0 || (size_t)HP_TOK * J * sizeof(float) > 48 * 1024)
         return LUMEN_ERR_UNSUPPORTED;
     // few tokens: a head's outputs are spread over more blocks, so that the step fills the device
@@ -291,16 +306,15 @@ LUMEN_API int lumen_head_product(const float* x, const void* w, int w_is_bf16, v
     const size_t smem = (size_t)HP_TOK * J * sizeof(float);
     if (w_is_bf16 && out_is_bf16)
         lumen_launch(head_product_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), smem, stream, x,
-                     (const __nv_bfloat16*)w, (__nv_bfloat16*)out, N, H, J, E);
+                     (const __nv_bfloat16*)w, (__nv_bfloat16*)out, N, H, J, E, hg);
     else if (w_is_bf16)
         lumen_launch(head_product_kernel<__nv_bfloat16, float>, grid, dim3(256), smem, stream, x, (const __nv_bfloat16*)w,
-                     (float*)out, N, H, J, E);
+                     (float*)out, N, H, J, E, hg);
     else if (out_is_bf16)
         lumen_launch(head_product_kernel<float, __nv_bfloat16>, grid, dim3(256), smem, stream, x, (const float*)w,
-                     (__nv_bfloat16*)out, N, H, J, E);
+                     (__nv_bfloat16*)out, N, H, J, E, hg);
     else
-        lumen_launch(head_product_kernel<float, float>, grid, dim3(256), smem, stream, x, (const float*)w, (float*)out, N,
-                     H, J, E);
+        lumen_launch(head_product_kernel<float, float>, grid, dim3(256), smem, stream, x, (const float*)w, (float*)out, N, H, J, E, hg);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -322,7 +336,7 @@ template <bool B_KN>
 __global__ void __launch_bounds__(128)
 head_gemm_kernel(const float* __restrict__ x, int S, size_t split_stride, long long xrs, int xhs,
                  const __nv_bfloat16* __restrict__ w, int ldw, long long w_head_stride, __nv_bfloat16* __restrict__ out,
-                 long long ors, int ohs, int N, int J, int E) {
+                 long long ors, int ohs, int N, int J, int E, HeadGate hg) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) __nv_bfloat16 As[HG_M * HG_LDA];
@@ -418,12 +432,13 @@ head_gemm_kernel(const float* __restrict__ x, int S, size_t split_stride, long l
     }
     const int g = lane >> 2, t = lane & 3;
     const int r0 = n0 + 16 * warp + g, r1 = r0 + 8;
+    const float g0v = r0 < N ? hg.of(r0, h) : 1.0f, g1v = r1 < N ? hg.of(r1, h) : 1.0f;
 #pragma unroll
     for (int nt = 0; nt < HG_N / 8; ++nt) {
         const int e = e0 + 8 * nt + 2 * t;
         if (e < E) {
-            if (r0 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][0], acc[nt][1]);
-            if (r1 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][2], acc[nt][3]);
+            if (r0 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r0 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][0] * g0v, acc[nt][1] * g0v);
+            if (r1 < N) *reinterpret_cast<uint32_t*>(out + (size_t)r1 * ors + (size_t)h * ohs + e) = pack_bf16(acc[nt][2] * g1v, acc[nt][3] * g1v);
         }
     }
 }
@@ -439,18 +454,21 @@ LUMEN_API int lumen_head_gemm_takes(long long xrs, int xhs, long long split_stri
 // b_kn 1: B_h = w + h w_head_stride is [J][E] with rows ldw apart; 0: [E][J].
 LUMEN_API int lumen_head_gemm(const float* x, int n_split, long long split_stride, long long xrs, int xhs, const void* w,
                               int b_kn, int ldw, long long w_head_stride, void* out, long long ors, int ohs, int N, int H,
-                              int J, int E, cudaStream_t stream) {
+                              int J, int E, const float* gate, int gate_split, long long gate_split_stride, int gate_w,
+                              int gate_col, cudaStream_t stream) {
     if (N <= 0) return 0;
+    if (gate && (gate_split < 1 || gate_col < 0 || gate_col + H > gate_w)) return LUMEN_ERR_BAD_ARGUMENT;
+    const HeadGate hg = {gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col};
     if (H <= 0 || H > 65535 || n_split < 1 || (E + HG_N - 1) / HG_N > 65535 ||
         !lumen_head_gemm_takes(xrs, xhs, split_stride, ldw, w_head_stride, ors, ohs, J, E))
         return LUMEN_ERR_UNSUPPORTED;
     dim3 grid((N + HG_M - 1) / HG_M, (E + HG_N - 1) / HG_N, H);
     if (b_kn)
         lumen_launch(head_gemm_kernel<true>, grid, dim3(128), 0, stream, x, n_split, (size_t)split_stride, xrs, xhs,
-                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E);
+                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E, hg);
     else
         lumen_launch(head_gemm_kernel<false>, grid, dim3(128), 0, stream, x, n_split, (size_t)split_stride, xrs, xhs,
-                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E);
+                     (const __nv_bfloat16*)w, ldw, w_head_stride, (__nv_bfloat16*)out, ors, ohs, N, J, E, hg);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -613,6 +631,139 @@ LUMEN_API int lumen_head_norm_gate(const float* y, const float* w, float eps, co
     else
         lumen_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, y, w, eps, gate, n_split,
                      (size_t)split_stride, Wg, g0, (float*)out, N, H, E);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- further element-wise pieces
+// out = max(z, 0)^2; z as partial sums [S, total].
+template <typename TO>
+__global__ void relu2_kernel(const float* __restrict__ z, int S, size_t split_stride, TO* __restrict__ out,
+                             long long total) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(parts_sum(z + i, S, split_stride), 0.0f);
+        out[i] = from_f32<TO>(v * v);
+    }
+}
+
+LUMEN_API int lumen_relu2(const float* z, int n_split, long long split_stride, void* out, int out_is_bf16,
+                          long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (n_split < 1) return LUMEN_ERR_BAD_ARGUMENT;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_is_bf16)
+        lumen_launch(relu2_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, z, n_split,
+                     (size_t)split_stride, (__nv_bfloat16*)out, total);
+    else
+        lumen_launch(relu2_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, n_split, (size_t)split_stride,
+                     (float*)out, total);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// A gated unit with clamped halves: row n of u (partial sums [S, N, W]) holds F gate values, then F
+// up values; g = min(gate, limit), v = clamp(up, -limit, limit), out[n, f] = g sigmoid(alpha g) (v + 1),
+// times sigmoid(u[n, tg]) when tg >= 0 (one gate a token, a further column of the same row).
+__device__ __forceinline__ float clamped_glu_f(float g, float v, float limit, float alpha) {
+    g = fminf(g, limit);
+    v = fminf(fmaxf(v, -limit), limit);
+    return g * sigmoid_f(alpha * g) * (v + 1.0f);
+}
+template <typename TO>
+__global__ void clamped_glu_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int F, float limit,
+                                   float alpha, int tg, TO* __restrict__ out, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / F;
+        const int f = (int)(i - n * F);
+        const float* row = u + n * W;
+        float y = clamped_glu_f(parts_sum(row + f, S, split_stride), parts_sum(row + F + f, S, split_stride), limit, alpha);
+        if (tg >= 0) y *= sigmoid_f(parts_sum(row + tg, S, split_stride));
+        out[i] = from_f32<TO>(y);
+    }
+}
+
+LUMEN_API int lumen_clamped_glu(const float* u, int n_split, long long split_stride, int W, int F, float limit,
+                                float alpha, int token_gate_col, void* out, int out_is_bf16, int N,
+                                cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_split < 1 || F <= 0 || 2 * F > W || token_gate_col >= W) return LUMEN_ERR_BAD_ARGUMENT;
+    const long long total = (long long)N * F;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_is_bf16)
+        lumen_launch(clamped_glu_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, u, n_split,
+                     (size_t)split_stride, W, F, limit, alpha, token_gate_col, (__nv_bfloat16*)out, total);
+    else
+        lumen_launch(clamped_glu_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, u, n_split,
+                     (size_t)split_stride, W, F, limit, alpha, token_gate_col, (float*)out, total);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// out[n, c] = u[n, c0 + c] / sqrt(mean_c(u[n, c0 .. c0 + C]^2) + eps) * w[c]: an RMS norm of some
+// columns of a projection (partial sums [S, N, W]), in the run's type. A block a token.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+cols_rmsnorm_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int c0, int C,
+                    const float* __restrict__ w, float eps, TO* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const int n = blockIdx.x;
+    const float* src = u + (size_t)n * W + c0;
+    // a thread's values stay in registers where a row is at most 4 x 256 wide
+    float keep[4];
+    float ss = 0.0f;
+    int k = 0;
+    for (int c = threadIdx.x; c < C; c += 256, ++k) {
+        const float x = parts_sum(src + c, S, split_stride);
+        if (k < 4) keep[k] = x;
+        ss += x * x;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)C + eps);
+    k = 0;
+    for (int c = threadIdx.x; c < C; c += 256, ++k) {
+        const float x = k < 4 ? keep[k] : parts_sum(src + c, S, split_stride);
+        out[(size_t)n * C + c] = from_f32<TO>(x * inv * w[c]);
+    }
+}
+
+LUMEN_API int lumen_cols_rmsnorm(const float* u, int n_split, long long split_stride, int W, int c0, int C,
+                                 const float* w, float eps, void* out, int out_is_bf16, int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (n_split < 1 || C <= 0 || c0 < 0 || c0 + C > W) return LUMEN_ERR_BAD_ARGUMENT;
+    if (out_is_bf16)
+        lumen_launch(cols_rmsnorm_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride,
+                     W, c0, C, w, eps, (__nv_bfloat16*)out);
+    else
+        lumen_launch(cols_rmsnorm_kernel<float>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride, W, c0,
+                     C, w, eps, (float*)out);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// Logits in place: x <- x * scale, then, with cap > 0, x <- cap * tanh(x / cap).
+__global__ void scale_softcap_kernel(float* __restrict__ x, float scale, float cap, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
+}
+
+LUMEN_API int lumen_scale_softcap(float* x, float scale, float cap, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    lumen_launch(scale_softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, x, scale, cap, total);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

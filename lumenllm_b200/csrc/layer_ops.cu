@@ -711,3 +711,89 @@ LUMEN_API int lumen_qkv_bias_norm_store(const float* qkv, int n_split, long long
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------- scaled updates + Dynamic Tanh
+// x = h[r] + sum over groups g, over the group's partial sums s, of scale_g * delta_g[s][r] (groups
+// and partial sums in rising order, float32); stored back to h[r] when write_h. Then, where y is
+// given, y = tanh(alpha * x) * w + b: a norm without a mean or a variance, so that a row needs no
+// reduction and a thread is done with its V values as soon as they are loaded. alpha is read
+// from device memory (one float). With `rows`, output row i is made from row rows[i]. With y null
+// the kernel only adds (any norm can then follow). Up to DYT_GROUPS groups a launch.
+#define DYT_GROUPS 4
+struct ScaledGroups {
+    const float* p[DYT_GROUPS];
+    long long stride[DYT_GROUPS];      // between a group's partial sums, in floats
+    int S[DYT_GROUPS];
+    float scale[DYT_GROUPS];
+    int n;
+};
+
+template <typename TOut, int V>
+__global__ void __launch_bounds__(256)
+add_scaled_dyt_kernel(float* __restrict__ h, ScaledGroups gr, const float* __restrict__ w, const float* __restrict__ b,
+                      const float* __restrict__ alpha, TOut* __restrict__ y, const int* __restrict__ rows, int H,
+                      int write_h) {
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    Vals<V> wv, bv;
+    float a = 0.0f;
+    if (y && i < H) {            // the norm's own numbers never change: they are read before the wait
+        wv = ldv<V>(w + i);
+        bv = ldv<V>(b + i);
+        a = *alpha;
+    }
+    pdl_trigger();
+    pdl_wait();
+    if (i >= H) return;
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* hr = h + (size_t)r * H + i;
+    Vals<V> x = ldv<V>(hr);
+    bool any = false;
+    for (int g = 0; g < gr.n; ++g) {
+        const float* d = gr.p[g] + (size_t)r * H + i;
+        const float sc = gr.scale[g];
+        for (int s = 0; s < gr.S[g]; ++s) {
+            const Vals<V> dv = ldv<V>(d + (size_t)s * gr.stride[g]);
+#pragma unroll
+            for (int k = 0; k < V; ++k) x.v[k] = fmaf(sc, dv.v[k], x.v[k]);
+            any = true;
+        }
+    }
+    if (write_h && any) stv<V>(hr, x);
+    if (!y) return;
+    Vals<V> o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = fmaf(tanhf(a * x.v[k]), wv.v[k], bv.v[k]);
+    stv<V>(y + (size_t)blockIdx.x * H + i, o);
+}
+
+// ptrs / strides / counts / scales: host arrays of n_groups entries.
+LUMEN_API int lumen_add_scaled_dyt(float* h, const void* const* ptrs, const long long* strides, const int* counts,
+                                   const float* scales, int n_groups, const float* w, const float* b,
+                                   const float* alpha, void* y, int y_is_bf16, const int* rows, int n_rows, int H,
+                                   int write_h, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || n_groups < 0 || n_groups > DYT_GROUPS || (y && (!w || !b || !alpha))) return LUMEN_ERR_BAD_ARGUMENT;
+    ScaledGroups gr = {};
+    gr.n = n_groups;
+    bool vec = (H & 3) == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+               (!y || (((uintptr_t)w & 15) == 0 && ((uintptr_t)b & 15) == 0));
+    for (int g = 0; g < n_groups; ++g) {
+        gr.p[g] = (const float*)ptrs[g];
+        gr.stride[g] = strides[g];
+        gr.S[g] = counts[g];
+        gr.scale[g] = scales[g];
+        if (counts[g] < 0 || (counts[g] > 0 && !ptrs[g])) return LUMEN_ERR_BAD_ARGUMENT;
+        if (((uintptr_t)ptrs[g] & 15) || (strides[g] & 3)) vec = false;
+    }
+    const int per = vec ? 4 : 1;
+    int threads = (((H + per - 1) / per + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    dim3 grid(n_rows, (H + per * threads - 1) / (per * threads));
+    if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
+#define DYT_GO(T, V_) lumen_launch(add_scaled_dyt_kernel<T, V_>, grid, dim3(threads), 0, stream, h, gr, w, b, alpha, (T*)y, rows, H, write_h)
+    if (y_is_bf16) { if (vec) DYT_GO(__nv_bfloat16, 4); else DYT_GO(__nv_bfloat16, 1); }
+    else { if (vec) DYT_GO(float, 4); else DYT_GO(float, 1); }
+#undef DYT_GO
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}

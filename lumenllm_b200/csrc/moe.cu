@@ -1,13 +1,18 @@
 // A feed-forward made of many small experts of which each token uses a few.
-//   1. route: softmax over the router's logits (float32), choice by score + a correction, the
-//      chosen experts' scores (without the correction) times a scale as weights.
+//   1. route: softmax over the router's logits (float32) or, mode 1, a sigmoid of each logit by
+//      itself; choice by score + a correction, the chosen experts' scores (without the correction)
+//      times a scale as weights.
 //   2. group: the step's (token, choice) entries put in order of their expert, and the list of
 //      row tiles (expert, first entry, number of entries) that the products walk. Everything
 //      stays on the device: the products are launched with as many blocks as any routing can
 //      need, and the blocks beyond the list leave.
 //   3. two grouped products: gate and up with SiLU(gate) * up behind them, then down with the
 //      entry's weight, written to out[choice][token][:] so that the consumer adds a token's
-//      choices in rising order, like the partial sums of a split product.
+//      choices in rising order, like the partial sums of a split product. The entry's weight may
+//      multiply the expert's INPUT instead: the gated product then multiplies its two sums by it
+//      before the activation (a product is linear in its input), and the down product gets no
+//      weights. Activation 1 is the clamped unit g sigmoid(alpha g) (v + 1) with g = min(gate, limit),
+//      v = clamp(up, -limit, limit).
 //   4. identity experts (indices from n_experts on): out[choice][token][:] = weight * input,
 //      written by the routing kernel, which has the token's row at hand.
 // Every output element is one dot product summed over k in rising order by one thread, so it
@@ -28,9 +33,18 @@
 // A warp a token. logits float32 [N, Et]; corr float32 [Et] or null; idx int32 [N, top];
 // wt float32 [N, top]. Equal choice scores go to the lower index.
 __device__ __forceinline__ void route_row(const float* __restrict__ lg, const float* __restrict__ corr, int Et,
-                                          int top, float scale, int* __restrict__ idx, float* __restrict__ wt, int lane) {
+                                          int top, float scale, int* __restrict__ idx, float* __restrict__ wt, int lane,
+                                          int mode) {
     float s[MOE_MAX_LANE_VALS], c[MOE_MAX_LANE_VALS];
     float m = -INFINITY;
+    if (mode == 1) {            // every score by itself: 1 / (1 + exp(-logit))
+#pragma unroll
+        for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
+            const int e = lane + 32 * r;
+            s[r] = e < Et ? 1.0f / (1.0f + expf(-lg[e])) : 0.0f;
+            c[r] = e < Et ? s[r] + (corr ? corr[e] : 0.0f) : -INFINITY;
+        }
+    } else {
 #pragma unroll
     for (int r = 0; r < MOE_MAX_LANE_VALS; ++r) {
         const int e = lane + 32 * r;
@@ -52,6 +66,7 @@ __device__ __forceinline__ void route_row(const float* __restrict__ lg, const fl
         const int e = lane + 32 * r;
         s[r] *= inv;
         c[r] = e < Et ? s[r] + (corr ? corr[e] : 0.0f) : -INFINITY;
+    }
     }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY, best_s = 0.0f;
@@ -80,13 +95,13 @@ __device__ __forceinline__ void route_row(const float* __restrict__ lg, const fl
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ corr, int Et, int top, float scale,
-                 int* __restrict__ idx, float* __restrict__ wt, int N) {
+                 int* __restrict__ idx, float* __restrict__ wt, int N, int mode) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= N) return;
-    route_row(logits + (size_t)t * Et, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+    route_row(logits + (size_t)t * Et, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane, mode);
 }
 
 // The router's product and the choice in one kernel, a block a token: the token's row goes to
@@ -97,7 +112,7 @@ template <typename TA>
 __global__ void __launch_bounds__(1024)
 moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K, const float* __restrict__ corr, int Et,
                    int top, float scale, int* __restrict__ idx, float* __restrict__ wt, float* __restrict__ ident_out,
-                   int E, int n_tokens) {
+                   int E, int n_tokens, int mode) {
     extern __shared__ __align__(16) float rs[];      // K floats, then Et logits
     pdl_trigger();
     pdl_wait();
@@ -127,7 +142,7 @@ moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K,
         if (lane == 0) lg[e] = acc;
     }
     __syncthreads();
-    if (warp == 0) route_row(lg, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+    if (warp == 0) route_row(lg, corr, Et, top, scale, idx + (size_t)t * top, wt + (size_t)t * top, lane, mode);
     if (!ident_out) return;
     // choices that fell on identity experts (indices from E on): the token's own row times the
     // weight, at the choice's place in the update's stack [top, tokens, K]
@@ -141,7 +156,8 @@ moe_route_x_kernel(const TA* __restrict__ x, const float* __restrict__ W, int K,
 }
 
 LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, int K, const float* corr, int Et, int top,
-                                float scale, int* idx, float* wt, float* ident_out, int E, int N, cudaStream_t stream) {
+                                float scale, int* idx, float* wt, float* ident_out, int E, int N, int mode,
+                                cudaStream_t stream) {
     if (N <= 0) return 0;
     if (Et <= 0 || top <= 0 || top > Et || K <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(K + Et) * sizeof(float);
@@ -153,23 +169,23 @@ LUMEN_API int lumen_moe_route_x(const void* x, int x_is_bf16, const float* W, in
         auto k = moe_route_x_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, (const __nv_bfloat16*)x, W, K, corr, Et, top, scale, idx, wt,
-                     ident_out, E, N);
+                     ident_out, E, N, mode);
     } else {
         auto k = moe_route_x_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         lumen_launch(k, dim3(N), dim3(threads), smem, stream, (const float*)x, W, K, corr, Et, top, scale, idx, wt, ident_out,
-                     E, N);
+                     E, N, mode);
     }
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
 
 LUMEN_API int lumen_moe_route(const float* logits, const float* corr, int Et, int top, float scale, int* idx,
-                              float* wt, int N, cudaStream_t stream) {
+                              float* wt, int N, int mode, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (Et <= 0 || top <= 0 || top > Et) return LUMEN_ERR_BAD_ARGUMENT;
     if (Et > 32 * MOE_MAX_LANE_VALS) return LUMEN_ERR_UNSUPPORTED;
-    lumen_launch(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, stream, logits, corr, Et, top, scale, idx, wt, N);
+    lumen_launch(moe_route_kernel, dim3((N + 3) / 4), dim3(128), 0, stream, logits, corr, Et, top, scale, idx, wt, N, mode);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -234,15 +250,28 @@ LUMEN_API int lumen_moe_group(const int* idx, int entries, int E, int tile_rows,
 // ---------------------------------------------------------------- grouped products
 // Block (tile, column block): the tile's entries x MOE_TN output columns of the tile's expert.
 // GATED: the rows of the activations are tokens (entry / top); W is [E, 2 F, K], gate rows
-//   first; out[entry, f] = silu(gate) * up, in the activations' type.
+//   first; out[entry, f] = act(w gate, w up) in the activations' type, w the entry's weight (1
+//   when wt is null), act = silu(gate) * up or the clamped unit (MoeAct).
 // else:  the rows of the activations are entries; W is [E, Nout, K]; out is float32
 //   [top, tokens, Nout] and receives weight[entry] * product at [entry % top][entry / top].
 // 256 threads; a thread holds 2 rows x 4 columns (of gate and of up when GATED).
+struct MoeAct {
+    int kind;            // 0: silu(g) * u; 1: min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) + 1)
+    float limit, alpha;
+    __device__ __forceinline__ float of(float g, float u) const {
+        if (kind == 1) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+        }
+        return g / (1.0f + expf(-g)) * u;
+    }
+};
 template <typename TA, typename TW, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const int* __restrict__ sorted,
                    const int* __restrict__ tiles, const int* __restrict__ n_tiles, const float* __restrict__ wt,
-                   void* __restrict__ out, int K, int Nout, int top, int n_tokens) {
+                   void* __restrict__ out, int K, int Nout, int top, int n_tokens, MoeAct act) {
     __shared__ float As[MOE_TK][MOE_TM + 1];
     __shared__ float Ws[GATED ? 2 : 1][MOE_TK][MOE_TN + 1];
     __shared__ int rows[MOE_TM];
@@ -299,15 +328,16 @@ moe_product_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const int
     for (int i = 0; i < 2; ++i) {
         const int entry = rows[ty * 2 + i];
         if (entry < 0) continue;
+        const float we = wt ? wt[entry] : 1.0f;
 #pragma unroll
         for (int jn = 0; jn < 4; ++jn) {
             const int n = n0 + tx * 4 + jn;
             if (n >= Nout) continue;
             if (GATED) {
-                const float g = acc[0][i][jn], u = acc[GATED ? 1 : 0][i][jn];
-                ((TA*)out)[(size_t)entry * Nout + n] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
+                const float g = we * acc[0][i][jn], u = we * acc[GATED ? 1 : 0][i][jn];
+                ((TA*)out)[(size_t)entry * Nout + n] = from_f32<TA>(act.of(g, u));
             } else {
-                ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = wt[entry] * acc[0][i][jn];
+                ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = we * acc[0][i][jn];
             }
         }
     }
@@ -327,7 +357,8 @@ template <bool GATED, int MI>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                        const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles,
-                       const float* __restrict__ wt, void* __restrict__ out, int K, int Nout, int top, int n_tokens) {
+                       const float* __restrict__ wt, void* __restrict__ out, int K, int Nout, int top, int n_tokens,
+                       MoeAct act) {
     constexpr int NM = GATED ? 2 : 1;
     constexpr int TM = 16 * MI;
     __shared__ __align__(16) __nv_bfloat16 As[TM * MOE_LD];
@@ -426,18 +457,19 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
         for (int hf = 0; hf < 2; ++hf) {
             const int entry = rows[mi * 16 + (lane >> 2) + hf * 8];
             if (entry < 0) continue;
+            const float we = wt ? wt[entry] : 1.0f;
 #pragma unroll
             for (int ni = 0; ni < 2; ++ni)
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     const int n = n0 + warp * 16 + ni * 8 + 2 * (lane & 3) + x;
                     if (n >= Nout) continue;
-                    const float v = acc[0][mi][ni][hf * 2 + x];
+                    const float v = we * acc[0][mi][ni][hf * 2 + x];
                     if (GATED) {
-                        const float u = acc[NM - 1][mi][ni][hf * 2 + x];
-                        ((__nv_bfloat16*)out)[(size_t)entry * Nout + n] = __float2bfloat16_rn(v / (1.0f + expf(-v)) * u);
+                        const float u = we * acc[NM - 1][mi][ni][hf * 2 + x];
+                        ((__nv_bfloat16*)out)[(size_t)entry * Nout + n] = __float2bfloat16_rn(act.of(v, u));
                     } else {
-                        ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = wt[entry] * v;
+                        ((float*)out)[((size_t)(entry % top) * n_tokens + entry / top) * Nout + n] = v;
                     }
                 }
         }
@@ -447,9 +479,11 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16*
 // gated == 0: A [entries, K] -> out float32 [top, tokens, Nout], W [E, Nout, K].
 LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int w_is_bf16, const int* sorted,
                                 const int* tiles, const int* n_tiles, int max_tiles, const float* wt, void* out,
-                                int K, int Nout, int top, int n_tokens, int gated, int tensor_cores,
-                                cudaStream_t stream) {
+                                int K, int Nout, int top, int n_tokens, int gated, int tensor_cores, int act_kind,
+                                float act_limit, float act_alpha, cudaStream_t stream) {
     if (max_tiles <= 0 || n_tokens <= 0) return 0;
+    if (act_kind < 0 || act_kind > 1) return LUMEN_ERR_BAD_ARGUMENT;
+    const MoeAct act = {act_kind, act_limit, act_alpha};
     if (K <= 0 || Nout <= 0 || top <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     dim3 grid(max_tiles, (Nout + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
@@ -458,7 +492,7 @@ LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int
         if (!a_is_bf16 || !w_is_bf16 || (K & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return LUMEN_ERR_UNSUPPORTED;
 #define MOE_MMA_GO(G_, MI_)                                                                                     \
     lumen_launch(moe_product_mma_kernel<G_, MI_>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A,          \
-                 (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens)
+                 (const __nv_bfloat16*)W, sorted, tiles, n_tiles, wt, out, K, Nout, top, n_tokens, act)
         if (tensor_cores == 2) { if (gated) MOE_MMA_GO(true, 1); else MOE_MMA_GO(false, 1); }
         else { if (gated) MOE_MMA_GO(true, 4); else MOE_MMA_GO(false, 4); }
 #undef MOE_MMA_GO
@@ -467,7 +501,7 @@ LUMEN_API int lumen_moe_product(const void* A, int a_is_bf16, const void* W, int
     }
 #define MOE_GO(TA, TW, GATED)                                                                                        \
     lumen_launch(moe_product_kernel<TA, TW, GATED>, grid, dim3(256), 0, stream, (const TA*)A, (const TW*)W, sorted, \
-                 tiles, n_tiles, wt, out, K, Nout, top, n_tokens)
+                 tiles, n_tiles, wt, out, K, Nout, top, n_tokens, act)
     if (a_is_bf16 && w_is_bf16) { if (gated) MOE_GO(__nv_bfloat16, __nv_bfloat16, true); else MOE_GO(__nv_bfloat16, __nv_bfloat16, false); }
     else if (!a_is_bf16 && w_is_bf16) { if (gated) MOE_GO(float, __nv_bfloat16, true); else MOE_GO(float, __nv_bfloat16, false); }
     else if (!a_is_bf16 && !w_is_bf16) { if (gated) MOE_GO(float, float, true); else MOE_GO(float, float, false); }

@@ -411,10 +411,14 @@ def moe_takes_tensor_cores(a_dtype, w) -> bool:
     return (a_dtype == BF16 and w.dtype == BF16 and w.shape[2] % 8 == 0 and w.data_ptr() % 16 == 0)
 
 
-def moe_route(logits, correction, top, scale):
-    """Softmax over a token's router logits (float32 [N, E]), the `top` experts with the largest
-    score + correction (equal ones: the lower index), and their scores (without the correction)
-    times `scale` as weights. Returns (idx int32 [N, top], weights float32 [N, top])."""
+ROUTER_MODES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_route(logits, correction, top, scale, mode="softmax"):
+    """Softmax over a token's router logits (float32 [N, E]) or, mode "sigmoid", a sigmoid of every
+    logit by itself; the `top` experts with the largest score + correction (equal ones: the lower
+    index), and their scores (without the correction) times `scale` as weights. Returns (idx int32
+    [N, top], weights float32 [N, top])."""
     require(logits, F32, "moe_route.logits")
     N, E = logits.shape
     if correction is not None:
@@ -423,12 +427,13 @@ def moe_route(logits, correction, top, scale):
             raise KernelError(f"moe_route: the correction must have {E} values")
     idx = torch.empty((N, top), dtype=I32, device=logits.device)
     wt = torch.empty((N, top), dtype=F32, device=logits.device)
-    f = fn("moe", "lumen_moe_route", [P, P, c_int, c_int, c_float, P, P, c_int, P])
-    check(f(ptr(logits), ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt), N, stream_ptr()), "moe_route")
+    f = fn("moe", "lumen_moe_route", [P, P, c_int, c_int, c_float, P, P, c_int, c_int, P])
+    check(f(ptr(logits), ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt), N, ROUTER_MODES[mode],
+            stream_ptr()), "moe_route")
     return idx, wt
 
 
-def moe_route_x(x, router, correction, top, scale, identity_out=None, n_experts=0):
+def moe_route_x(x, router, correction, top, scale, identity_out=None, n_experts=0, mode="softmax"):
     """moe_route with the router's product in the same kernel: x [N, K] in the run's type, router
     float32 [E, K]; the logits are float32 sums over float32(x) * router. With identity_out
     (float32 [top, N, K]) the choices whose index is >= n_experts are filled in there at once:
@@ -448,9 +453,9 @@ def moe_route_x(x, router, correction, top, scale, identity_out=None, n_experts=
             raise KernelError(f"moe_route_x: identity_out {tuple(identity_out.shape)} is not [{top}, {N}, {Kw}]")
     idx = torch.empty((N, top), dtype=I32, device=x.device)
     wt = torch.empty((N, top), dtype=F32, device=x.device)
-    f = fn("moe", "lumen_moe_route_x", [P, c_int, P, c_int, P, c_int, c_int, c_float, P, P, P, c_int, c_int, P])
+    f = fn("moe", "lumen_moe_route_x", [P, c_int, P, c_int, P, c_int, c_int, c_float, P, P, P, c_int, c_int, c_int, P])
     check(f(ptr(x), _is_bf16(x), ptr(router), Kw, ptr(correction), E, int(top), float(scale), ptr(idx), ptr(wt),
-            ptr(identity_out), int(n_experts), N, stream_ptr()), "moe_route_x")
+            ptr(identity_out), int(n_experts), N, ROUTER_MODES[mode], stream_ptr()), "moe_route_x")
     return idx, wt
 
 
@@ -474,12 +479,15 @@ def moe_group(idx, n_experts, tensor_cores=False):
     return sorted_, tiles, n_tiles, max_tiles, tensor_cores
 
 
-def moe_product(a, w, group, weights, top, n_tokens, gated, out=None):
+def moe_product(a, w, group, weights, top, n_tokens, gated, out=None, clamp=None):
     """A grouped product over the tiles of moe_group. gated: a [tokens, K] in the run's type, w
-    [E, 2 F, K] (gate rows, then up rows) -> silu(gate) * up as [entries, F] in a's type. Not
-    gated: a [entries, K], w [E, D, K] -> float32 [top, tokens, D] with every entry's product
-    times its weight at [choice][token] (into `out` when given); rows of entries that are left
-    out (identity experts) are not written."""
+    [E, 2 F, K] (gate rows, then up rows) -> silu(gate) * up as [entries, F] in a's type; with
+    `weights` both sums are multiplied by the entry's weight first (the weight on the expert's
+    input), with clamp = (limit, alpha) the activation is g sigmoid(alpha g) (v + 1), g = min(gate,
+    limit), v = clamp(up, -limit, limit). Not gated: a [entries, K], w [E, D, K] -> float32 [top,
+    tokens, D] with every entry's product times its weight (1 without `weights`) at [choice][token]
+    (into `out` when given); rows of entries that are left out (identity experts) are not
+    written."""
     sorted_, tiles, n_tiles, max_tiles, tensor_cores = group
     E, rows, K = w.shape
     if tensor_cores and not (moe_takes_tensor_cores(a.dtype, w) and a.data_ptr() % 16 == 0):
@@ -493,16 +501,20 @@ def moe_product(a, w, group, weights, top, n_tokens, gated, out=None):
         out = torch.empty((n_tokens * top, n_out), dtype=a.dtype, device=a.device)
     else:
         n_out = rows
-        require(weights, F32, "moe_product.weights")
         if out is None:
             out = torch.empty((top, n_tokens, n_out), dtype=F32, device=a.device)
         elif out.dtype != F32 or tuple(out.shape) != (top, n_tokens, n_out) or not out.is_contiguous():
             raise KernelError(f"moe_product: out {tuple(out.shape)} is not float32 [{top}, {n_tokens}, {n_out}]")
+    if weights is not None:
+        require(weights, F32, "moe_product.weights")
+        if weights.numel() != n_tokens * top:
+            raise KernelError(f"moe_product: {weights.numel()} weights for {n_tokens * top} entries")
+    limit, alpha = (0.0, 1.0) if clamp is None else clamp
     f = fn("moe", "lumen_moe_product", [P, c_int, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
-                                        c_int, P])
+                                        c_int, c_int, c_float, c_float, P])
     check(f(ptr(a), _is_bf16(a), ptr(w), _is_bf16(w), ptr(sorted_), ptr(tiles), ptr(n_tiles), int(max_tiles),
             ptr(weights), ptr(out), K, n_out, int(top), int(n_tokens), 1 if gated else 0, int(tensor_cores),
-            stream_ptr()), "moe_product")
+            0 if clamp is None else 1, float(limit), float(alpha), stream_ptr()), "moe_product")
     return out
 
 
@@ -546,14 +558,14 @@ def silu_mul(gu, out_dtype, interleaved=False):
     return z
 
 
-def rope_table(positions, inv_freq):
-    """(cos, sin) of float32(pos) * inv_freq: float32 [N, rot/2, 2]."""
+def rope_table(positions, inv_freq, magnitude=1.0):
+    """magnitude * (cos, sin) of float32(pos) * inv_freq: float32 [N, rot/2, 2]."""
     require(positions, I32, "rope_table.positions")
     require(inv_freq, F32, "rope_table.inv_freq")
     N, half = positions.numel(), inv_freq.numel()
     cs = torch.empty((N, half, 2), dtype=F32, device=positions.device)
-    f = fn("core", "lumen_rope_table", [P, P, P, c_int, c_int, P])
-    check(f(ptr(positions), ptr(inv_freq), ptr(cs), N, half, stream_ptr()), "rope_table")
+    f = fn("core", "lumen_rope_table", [P, P, P, c_int, c_int, c_float, P])
+    check(f(ptr(positions), ptr(inv_freq), ptr(cs), N, half, float(magnitude), stream_ptr()), "rope_table")
     return cs
 
 
@@ -802,7 +814,7 @@ def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim, out_dtype=F
         # the products on the tensor cores; the kernel below then only moves and rotates the rest
         g = fn("head_ops", "lumen_head_gemm", _HEAD_GEMM_ARGS)
         check(g(ptr(q), S, N * W, W, d + rot_width, ptr(up_k), 1, rank, d * rank, ptr(out), heads * Wo, Wo, N,
-                int(heads), int(d), int(rank), stream_ptr()), "head_gemm")
+                int(heads), int(d), int(rank), *_NO_HEAD_GATE, stream_ptr()), "head_gemm")
         product = 0
     f = fn("head_ops", "lumen_latent_query",
            [P, c_int, c_longlong, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P, c_int, c_int, c_int, P])
@@ -813,7 +825,8 @@ def latent_query(q, up_k, heads, d, rot_width, rank, cs, rotary_dim, out_dtype=F
 
 
 _HEAD_GEMM_ARGS = [P, c_int, c_longlong, c_longlong, c_int, P, c_int, c_int, c_longlong, P, c_longlong, c_int, c_int,
-                   c_int, c_int, c_int, P]
+                   c_int, c_int, c_int, P, c_int, c_longlong, c_int, c_int, P]
+_NO_HEAD_GATE = (0, 0, 0, 0, 0)
 
 
 def _head_gemm_takes(xrs, xhs, split_stride, ldw, w_head_stride, ors, ohs, J, E) -> bool:
@@ -871,22 +884,32 @@ def attn_latent(q, cache, block_table, cu_q, seq_start, q_lens, value_dim, windo
     return out
 
 
-def head_product(x, w, out_dtype):
+def head_product(x, w, out_dtype, gate=None, gate_col=0):
     """out[n, h, :] = w_h x[n, h, :] with w [heads * E, J] cut into `heads` matrices [E, J]; x float32
     [N, heads, J]; returns [N, heads * E] in out_dtype. In bfloat16, with J a multiple of 32 and E of
-    8, on the tensor cores (x rounded to bfloat16 as it is staged)."""
+    8, on the tensor cores (x rounded to bfloat16 as it is staged). With `gate` (float32 [N, W] or
+    partial sums) head h's output is multiplied by sigmoid(gate[n, gate_col + h]) before it is
+    rounded."""
     require(x, F32, "head_product.x")
     N, H, J = x.shape
+    hg = _NO_HEAD_GATE
+    if gate is not None:
+        gate, gS = _partials(gate, "head_product.gate")
+        if gate.shape[1] != N or gate_col + H > gate.shape[2]:
+            raise KernelError(f"head_product: gate {tuple(gate.shape)} has no {H} columns from {gate_col} for {N} tokens")
+        hg = (ptr(gate), gS, N * gate.shape[2], gate.shape[2], int(gate_col))
     if w.dim() != 2 or w.shape[1] != J or w.shape[0] % H or not w.is_contiguous():
         raise KernelError(f"head_product: weight {tuple(w.shape)} does not fit {H} heads of {J}")
     E = w.shape[0] // H
     out = torch.empty((N, H * E), dtype=out_dtype, device=x.device)
     if out_dtype == BF16 and w.dtype == BF16 and _head_gemm_takes(H * J, J, 0, J, E * J, H * E, E, J, E):
         g = fn("head_ops", "lumen_head_gemm", _HEAD_GEMM_ARGS)
-        check(g(ptr(x), 1, 0, H * J, J, ptr(w), 0, J, E * J, ptr(out), H * E, E, N, H, J, E, stream_ptr()), "head_gemm")
+        check(g(ptr(x), 1, 0, H * J, J, ptr(w), 0, J, E * J, ptr(out), H * E, E, N, H, J, E, *hg, stream_ptr()),
+              "head_gemm")
         return out
-    f = fn("head_ops", "lumen_head_product", [P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, P])
-    check(f(ptr(x), ptr(w), _is_bf16(w), ptr(out), _is_bf16(out), N, H, J, E, stream_ptr()), "head_product")
+    f = fn("head_ops", "lumen_head_product", [P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, P, c_int, c_longlong,
+                                              c_int, c_int, P])
+    check(f(ptr(x), ptr(w), _is_bf16(w), ptr(out), _is_bf16(out), N, H, J, E, *hg, stream_ptr()), "head_product")
     return out
 
 
@@ -897,6 +920,128 @@ def gelu_tanh(z, out_dtype):
     out = torch.empty((N, Fw), dtype=out_dtype, device=z.device)
     f = fn("head_ops", "lumen_gelu_tanh", [P, c_int, c_longlong, P, c_int, c_longlong, P])
     check(f(ptr(z), S, N * Fw, ptr(out), _is_bf16(out), N * Fw, stream_ptr()), "gelu_tanh")
+    return out
+
+
+def relu2(z, out_dtype):
+    """max(z, 0)^2; z float32 [N, F] or [S, N, F] partial sums."""
+    z, S = _partials(z, "relu2.z")
+    _, N, Fw = z.shape
+    out = torch.empty((N, Fw), dtype=out_dtype, device=z.device)
+    f = fn("head_ops", "lumen_relu2", [P, c_int, c_longlong, P, c_int, c_longlong, P])
+    check(f(ptr(z), S, N * Fw, ptr(out), _is_bf16(out), N * Fw, stream_ptr()), "relu2")
+    return out
+
+
+def clamped_glu(u, width, limit, alpha, out_dtype, token_gate_col=-1):
+    """A gated unit with clamped halves: u float32 [N, W] or partial sums, a row `width` gate values,
+    then `width` up values; g = min(gate, limit), v = clamp(up, -limit, limit); returns
+    g sigmoid(alpha g) (v + 1) as [N, width] in out_dtype, times sigmoid(u[n, token_gate_col]) where
+    that column is given (one gate a token)."""
+    u, S = _partials(u, "clamped_glu.u")
+    _, N, W = u.shape
+    if 2 * width > W or token_gate_col >= W:
+        raise KernelError(f"clamped_glu: rows of {W} do not hold two halves of {width} (and the gate's column)")
+    out = torch.empty((N, int(width)), dtype=out_dtype, device=u.device)
+    f = fn("head_ops", "lumen_clamped_glu", [P, c_int, c_longlong, c_int, c_int, c_float, c_float, c_int, P, c_int, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(width), float(limit), float(alpha), int(token_gate_col), ptr(out), _is_bf16(out), N,
+            stream_ptr()), "clamped_glu")
+    return out
+
+
+def cols_rmsnorm(u, col, width, weight, eps, out_dtype):
+    """Columns col .. col + width of u (float32 [N, W] or partial sums, added) divided by their root
+    mean square (sqrt(mean(x^2) + eps)) times weight [width], in out_dtype."""
+    u, S = _partials(u, "cols_rmsnorm.u")
+    _, N, W = u.shape
+    require(weight, F32, "cols_rmsnorm.weight")
+    if weight.numel() != width or col < 0 or col + width > W:
+        raise KernelError(f"cols_rmsnorm: {width} columns from {col} of rows of {W}, a weight of {weight.numel()}")
+    out = torch.empty((N, int(width)), dtype=out_dtype, device=u.device)
+    f = fn("head_ops", "lumen_cols_rmsnorm", [P, c_int, c_longlong, c_int, c_int, c_int, P, c_float, P, c_int, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(col), int(width), ptr(weight), float(eps), ptr(out), _is_bf16(out), N,
+            stream_ptr()), "cols_rmsnorm")
+    return out
+
+
+def scale_softcap(logits, scale, cap):
+    """In place: logits * scale, then, with cap > 0, cap * tanh(that / cap). float32, contiguous."""
+    require(logits, F32, "scale_softcap.logits")
+    f = fn("head_ops", "lumen_scale_softcap", [P, c_float, c_float, c_longlong, P])
+    check(f(ptr(logits), float(scale), float(cap or 0.0), logits.numel(), stream_ptr()), "scale_softcap")
+    return logits
+
+
+SCALED_GROUPS = 4      # groups of partial sums one launch of add_scaled_dyt takes
+
+
+def add_scaled_dyt(h, groups, weight, bias, alpha, out_dtype, rows=None, write_h=True):
+    """x = h + sum over (delta, scale) in `groups`, over delta's partial sums, of scale * delta[s]
+    (h float32 [N, H], updated in place when write_h; a delta float32 [N, H] or [S, N, H]); then
+    y = tanh(alpha * x) * weight + bias in out_dtype, alpha a float32 tensor of one value on the
+    device. With weight None nothing is normed and None is returned (the stream has its update);
+    rows int32 [W] gathers the rows to work on."""
+    require(h, F32, "add_scaled_dyt.h")
+    N, H = h.shape
+    groups = list(groups or ())
+    while len(groups) > SCALED_GROUPS:          # more groups than a launch takes: the first ones in launches of their own
+        add_scaled_dyt(h, groups[:SCALED_GROUPS], None, None, None, out_dtype)
+        groups = groups[SCALED_GROUPS:]
+    n = len(groups)
+    ptrs, strides, counts, scales = (c_void_p * max(n, 1))(), (c_longlong * max(n, 1))(), (c_int * max(n, 1))(), \
+        (c_float * max(n, 1))()
+    for g, (delta, scale) in enumerate(groups):
+        delta, S = _partials(delta, "add_scaled_dyt.delta")
+        if tuple(delta.shape[1:]) != (N, H):
+            raise KernelError(f"add_scaled_dyt: update {tuple(delta.shape)} does not fit the stream {(N, H)}")
+        ptrs[g], strides[g], counts[g], scales[g] = ptr(delta), N * H, S, float(scale)
+    n_rows, y = N, None
+    if rows is not None:
+        require(rows, I32, "add_scaled_dyt.rows")
+        n_rows = rows.numel()
+    if weight is not None:
+        for t, nm, k in ((weight, "weight", H), (bias, "bias", H), (alpha, "alpha", 1)):
+            require(t, F32, f"add_scaled_dyt.{nm}")
+            if t.numel() != k:
+                raise KernelError(f"add_scaled_dyt: {nm} has {t.numel()} values, not {k}")
+        y = torch.empty((n_rows, H), dtype=out_dtype, device=h.device)
+    elif n == 0:
+        return None
+    f = fn("layer_ops", "lumen_add_scaled_dyt", [P, P, P, P, P, c_int, P, P, P, P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(h), ptrs, strides, counts, scales, n, ptr(weight), ptr(bias), ptr(alpha), ptr(y),
+            _is_bf16(y) if y is not None else 0, ptr(rows), n_rows, H, 1 if write_h else 0, stream_ptr()),
+          "add_scaled_dyt")
+    return y
+
+
+def linear_attn_max_dim() -> int:
+    return int(int_fn("linear_attn", "lumen_linear_attn_max_dim", [])())
+
+
+def linear_attn(u, q_col, k_col, v_col, silu, decay, state, cu_q, seq_slot, n_seqs, heads, d, dv):
+    """Linear attention with a fixed decay a head (csrc/linear_attn.cu): S <- decay_h S + k v^T,
+    o = S^T q for every token in order. u: float32 [N, W] or partial sums with q and k (heads of d)
+    from q_col and k_col and v (heads of dv) from v_col, each through SiLU when `silu`; decay float32
+    [heads]; state float32 [slots, heads, d, dv] (row seq_slot[b] sequence b's, updated in place).
+    Returns float32 [N, heads * dv]."""
+    u, S = _partials(u, "linear_attn.u")
+    N, W = u.shape[1], u.shape[2]
+    require(decay, F32, "linear_attn.decay")
+    require(state, F32, "linear_attn.state", contiguous=False)
+    if decay.numel() != heads or tuple(state.shape[1:]) != (heads, d, dv) or not state[0].is_contiguous():
+        raise KernelError(f"linear_attn: decay of {decay.numel()}, state {tuple(state.shape)} do not fit {heads} heads of "
+                          f"{d} x {dv}")
+    require(cu_q, I32, "linear_attn.cu_q")
+    require(seq_slot, I32, "linear_attn.seq_slot")
+    if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs:
+        raise KernelError("linear_attn: metadata does not match the batch")
+    out = torch.empty((N, heads * dv), dtype=F32, device=u.device)
+    f = fn("linear_attn", "lumen_linear_attn",
+           [P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P, P, c_longlong, P, P, c_int, P, c_int, c_int,
+            c_int, P])
+    check(f(ptr(u), S, N * W, W, int(q_col), int(k_col), int(v_col), 1 if silu else 0, ptr(decay), ptr(state),
+            state.stride(0), ptr(cu_q), ptr(seq_slot), int(n_seqs), ptr(out), int(heads), int(d), int(dv), stream_ptr()),
+          "linear_attn")
     return out
 
 

@@ -6,7 +6,10 @@ The adds are not done here: a block hands its last update on as `pending`, and
 the next norm (the next block's, or the model's final one) adds it while it
 reads the stream anyway. A layer may lack the feed-forward (and its norm); with
 `extras["token_input"]` a part of that category (parts/token_input.py) runs after the
-sublayers and adds an input that comes from the tokens themselves.
+sublayers and adds an input that comes from the tokens themselves. With the layer's parameter
+`residual_scale` m != 1 every update counts m times, r = h + m mixer(..), h' = r + m ffn(..): the
+updates then go on as a ScaledUpdate (parts/norm.py), whose factors the next norm applies while it
+adds, and no part adds into the stream by itself.
 
 "parallel": h' = h + (mixer(norm(h)) + ffn(norm(h))): ONE norm, whose output both sublayers
 read; a layer may lack the feed-forward. The two updates go on side by side as one stack of
@@ -23,7 +26,7 @@ from __future__ import annotations
 import torch
 
 from .base import build_part, part_tensors, register_part
-from .norm import NormedUpdate
+from .norm import NormedUpdate, ScaledUpdate
 
 
 @register_part("block", "pre_norm")
@@ -50,6 +53,7 @@ class PreNormBlock:
             self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
         if "token_input" in layer_spec.extras:
             self.token_input = build_part("token_input", layer_spec.extras["token_input"], weights, runtime)
+        self.residual_scale = float(layer_spec.params.get("residual_scale", 1.0))
 
     @property
     def graph_safe(self):
@@ -60,17 +64,22 @@ class PreNormBlock:
         # there (a prompt-sized product does so in its epilogue) and return None, or return the
         # update as any part does. Either way the next norm sees the stream plus what is pending.
         y = self.norm_mixer.forward(h, pending, self.runtime.dtype)
-        if getattr(self.mixer, "adds_residual", False):
+        scaled = self.residual_scale != 1.0
+        if getattr(self.mixer, "adds_residual", False) and not scaled:
             a = self.mixer.forward(y, ctx, entry, residual=h)
         else:
             a = self.mixer.forward(y, ctx, entry)
+        if scaled or isinstance(a, (list, tuple)):
+            a = ScaledUpdate.of(a, self.residual_scale)
         m = a
         if self.ffn is not None:
             y2 = self.norm_ffn.forward(h, a, self.runtime.dtype)
-            if getattr(self.ffn, "adds_residual", False):
+            if getattr(self.ffn, "adds_residual", False) and not scaled:
                 m = self.ffn.forward(y2, ctx, residual=h)
             else:
                 m = self.ffn.forward(y2, ctx)
+            if scaled or isinstance(m, (list, tuple)):
+                m = ScaledUpdate.of(m, self.residual_scale)
         if self.token_input is not None:
             return self.token_input.forward(h, m, ctx)
         return h, m

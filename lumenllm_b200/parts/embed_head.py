@@ -53,7 +53,8 @@ class LinearHead:
     is used follows the reference, by presence (executor/full.rs:171-181): the head's own
     tensor when the file stores one, else the table named by `tied_to` or `falls_back_to`.
     So a tied checkpoint that also stores a head, and an untied one that stores none, both
-    load; the loader reports the second case in its `stood_in`."""
+    load; the loader reports the second case in its `stood_in`. With `logit_scale` s the logits
+    are multiplied by s, and with `softcap` c > 0 then bent to c tanh(logit / c), in float32."""
 
     @classmethod
     def tensors(cls, spec):
@@ -73,6 +74,11 @@ class LinearHead:
         if name is None or name not in weights:
             raise KeyError(f"the output head needs '{own}'")
         self.proj = Linear(weights[name], runtime)
+        self.logit_scale = float(spec.params.get("logit_scale", 1.0))
+        self.softcap = float(spec.params.get("softcap", 0.0) or 0.0)
 
     def forward(self, y):
-        return self.proj(y)
+        logits = self.proj(y)
+        if self.logit_scale != 1.0 or self.softcap > 0.0:
+            logits = K.scale_softcap(logits.contiguous(), self.logit_scale, self.softcap)
+        return logits
