@@ -7,12 +7,12 @@ HBM roofline of the decode step.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--timings]
-    python bench.py --design dabevik|rasezen|lebelix [--sizes 2k,4k] [--batch B] [--steps K] [--warmup W]
+    python bench.py --design dabevik|rasezen|lebelix|vekolix [--sizes 2k,4k] [--batch B] [--steps K] [--warmup W]
 
 `--shape` runs the same measurement at the two larger workloads (their batch, prompt
 lengths, context and sampling); `--timings` adds, from a separate pass that is not
 timed as a whole, each kernel class's share of a decode step and of a prompt step.
-`--design dabevik` (or `rasezen`, `lebelix`) measures that design beside the Qwen3 decoder at equal sizes instead (a few
+`--design dabevik` (or `rasezen`, `lebelix`, `vekolix`) measures that design beside the Qwen3 decoder at equal sizes instead (a few
 layers of real-model size, random weights: prompt and decode tokens per second, and each class
 of kernels' time in a step of either kind; lumenllm_b200/compare.py). The default workload and
 its JSON line are not touched by it.
@@ -357,7 +357,7 @@ def main() -> int:
                     help="context length (default: the workload's)")
     ap.add_argument("--prompt-len", default=None, metavar="LO:HI",
                     help="prompt lengths are drawn uniformly from this range")
-    ap.add_argument("--design", default=None, choices=["dabevik", "rasezen", "lebelix"],
+    ap.add_argument("--design", default=None, choices=["dabevik", "rasezen", "lebelix", "vekolix"],
                     help="measure this design beside the Qwen3 decoder at equal sizes instead of the benchmark")
     ap.add_argument("--sizes", default="2k,4k", help="with --design: which of compare.SIZES to run")
     args = ap.parse_args()

@@ -21,6 +21,13 @@ Lebelix's chunks and windows; what differs is the design: attention with capped 
 sink and an output gate, layers of latent attention (one of them reading an earlier layer's latent
 cache), layers whose mixer is the gated delta rule, a two-matrix GELU feed-forward, and the
 per-layer token input.
+
+Vekolix (`--design vekolix`, VEKOLIX_SIZES): the same width, layers, vocabulary, attention heads, kv
+heads, head size and dense feed-forward width, no window on either side; what differs is the design:
+Dynamic Tanh in place of the norms, a multiplier on every update, layers whose mixer is softmax
+attention and linear attention side by side, layers of latent attention with a query latent and a gate
+a head, a two-matrix squared-ReLU feed-forward, mixtures of clamped gated experts weighted on their
+input with a gated shared expert, and capped logits.
 """
 from __future__ import annotations
 
@@ -55,6 +62,19 @@ LEBELIX_SIZES = {
                latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512),
                delta=dict(heads=32, kv_heads=16, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128),
                side=256, pattern=["l", "a", "c", "L"]),
+}
+# Vekolix: layers as (mixer, feed-forward) pairs, "p" two mixers side by side, "l" latent attention; "d" dense, "e" experts
+VEKOLIX_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, window=0, vocab=32768, rot=64,
+               linear=dict(heads=16, dim=128, vdim=128),
+               latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768),
+               moe=dict(ff=1024, experts=16, top=4, limit=7.0, shared=2048, shared_limit=7.0),
+               pattern=["ld", "pe", "pd", "le", "pd", "pe", "ld", "pe"]),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, window=0, vocab=32768, rot=64,
+               linear=dict(heads=32, dim=128, vdim=128),
+               latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536),
+               moe=dict(ff=1536, experts=16, top=4, limit=7.0, shared=3072, shared_limit=7.0),
+               pattern=["ld", "pe", "pd", "le"]),
 }
 CONTEXT = 4096
 PROMPT_TOKENS = 2048
@@ -97,13 +117,32 @@ def lebelix_config(s):
                        for p in s["pattern"]]}
 
 
+def vekolix_config(s):
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "rot": {"base": 500000.0, "dims": s["rot"],
+                    "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    n = s["linear"]["heads"]
+    right = dict(s["linear"], decay=[1.0 - 2.0 ** (-2.0 - 8.0 * h / max(n - 1, 1)) for h in range(n)])
+    side = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.9}
+    lat = dict(s["latent"], scale=(s["latent"]["dim"] + s["latent"]["rot_dim"]) ** -0.5,
+               rot={"base": 1000000.0, "dims": s["latent"]["rot_dim"]})
+    m = s["moe"]
+    experts = {"kind": "moe", "expert": {"ff": m["ff"], "limit": m["limit"]},
+               "router": {"experts": m["experts"], "top": m["top"]},
+               "shared": {"ff": m["shared"], "limit": m["shared_limit"]}}
+    layers = [{"type": "parallel" if p[0] == "p" else "latent_attention", "mixer": side if p[0] == "p" else lat,
+               "mlp": {"kind": "dense", "ff": s["ff"]} if p[1] == "d" else experts} for p in s["pattern"]]
+    return {"architecture": "Vekolix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "residual_mult": 0.8, "logit_scale": 0.5, "logit_softcap": 30.0, "max_positions": CONTEXT, "layers": layers}
+
+
 def qwen3_config(s):
     n_layers = s["layers"] if "layers" in s else len(s["pattern"])
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=s["width"],
                 num_hidden_layers=n_layers, num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
                 head_dim=s["dim"], intermediate_size=s["ff"], vocab_size=s["vocab"], rope_theta=1000000.0,
                 rms_norm_eps=1e-6, max_position_embeddings=CONTEXT, tie_word_embeddings=True,
-                sliding_window=s["window"], layer_types=["sliding_attention"] * n_layers)
+                **({"sliding_window": s["window"], "layer_types": ["sliding_attention"] * n_layers} if s["window"] else {}))
 
 
 # kernel entry point -> class of kernels, for both designs
@@ -126,7 +165,10 @@ CLASSES = {
     "lumen_latent_store": "latent: norm + cache write", "lumen_latent_query": "latent: queries into the latent space",
     "lumen_head_product": "latent: values out of the latent space", "lumen_head_gemm": "latent: products of every head", "lumen_gelu_tanh": "activation",
     "lumen_token_gate": "token input", "lumen_add_cast": "token input", "lumen_cols_cast": "delta rule: low-rank inputs",
-    "lumen_delta_rule": "delta rule: recurrence", "lumen_head_norm_gate": "delta rule: norm + gate",
+    "lumen_delta_rule": "delta rule: recurrence", "lumen_head_norm_gate": "recurrence: norm + gate",
+    "lumen_add_scaled_dyt": "norm", "lumen_relu2": "activation", "lumen_clamped_glu": "activation",
+    "lumen_cols_rmsnorm": "norm of some columns (+ gate)", "lumen_scale_softcap": "logits: scale + cap",
+    "lumen_linear_attn": "linear attention: recurrence",
 }
 
 
@@ -222,7 +264,7 @@ def measure(config, batch, steps, warmup, seed=0):
 
 
 DESIGNS = {"dabevik": (SIZES, dabevik_config), "rasezen": (RASEZEN_SIZES, rasezen_config),
-           "lebelix": (LEBELIX_SIZES, lebelix_config)}
+           "lebelix": (LEBELIX_SIZES, lebelix_config), "vekolix": (VEKOLIX_SIZES, vekolix_config)}
 
 
 def sizes_of(design):

@@ -706,11 +706,13 @@ LUMEN_API int lumen_clamped_glu(const float* u, int n_split, long long split_str
 }
 
 // out[n, c] = u[n, c0 + c] / sqrt(mean_c(u[n, c0 .. c0 + C]^2) + eps) * w[c]: an RMS norm of some
-// columns of a projection (partial sums [S, N, W]), in the run's type. A block a token.
+// columns of a projection (partial sums [S, N, W]), in the run's type; with a gate (partial sums [gS, N,
+// gW]) also times sigmoid(gate[n, g0 + c]). A block a token.
 template <typename TO>
 __global__ void __launch_bounds__(256)
 cols_rmsnorm_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int c0, int C,
-                    const float* __restrict__ w, float eps, TO* __restrict__ out) {
+                    const float* __restrict__ w, float eps, TO* __restrict__ out, const float* __restrict__ gate, int gS,
+                    size_t g_split_stride, int gW, int g0) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
@@ -730,20 +732,25 @@ cols_rmsnorm_kernel(const float* __restrict__ u, int S, size_t split_stride, int
     k = 0;
     for (int c = threadIdx.x; c < C; c += 256, ++k) {
         const float x = k < 4 ? keep[k] : parts_sum(src + c, S, split_stride);
-        out[(size_t)n * C + c] = from_f32<TO>(x * inv * w[c]);
+        float y = x * inv * w[c];
+        if (gate) y *= sigmoid_f(parts_sum(gate + (size_t)n * gW + g0 + c, gS, g_split_stride));
+        out[(size_t)n * C + c] = from_f32<TO>(y);
     }
 }
 
 LUMEN_API int lumen_cols_rmsnorm(const float* u, int n_split, long long split_stride, int W, int c0, int C,
-                                 const float* w, float eps, void* out, int out_is_bf16, int N, cudaStream_t stream) {
+                                 const float* w, float eps, void* out, int out_is_bf16, int N, const float* gate,
+                                 int gate_split, long long gate_split_stride, int gate_w, int gate_col,
+                                 cudaStream_t stream) {
     if (N <= 0) return 0;
     if (n_split < 1 || C <= 0 || c0 < 0 || c0 + C > W) return LUMEN_ERR_BAD_ARGUMENT;
+    if (gate && (gate_split < 1 || gate_col < 0 || gate_col + C > gate_w)) return LUMEN_ERR_BAD_ARGUMENT;
     if (out_is_bf16)
         lumen_launch(cols_rmsnorm_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride,
-                     W, c0, C, w, eps, (__nv_bfloat16*)out);
+                     W, c0, C, w, eps, (__nv_bfloat16*)out, gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col);
     else
         lumen_launch(cols_rmsnorm_kernel<float>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride, W, c0,
-                     C, w, eps, (float*)out);
+                     C, w, eps, (float*)out, gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -5,18 +5,23 @@
 // in rising order where a value is read; with `act` 1 each value goes through SiLU first. State,
 // decay, sums and outputs are float32 whatever the run's type.
 //
-// A block takes one sequence, one head and LA_COLS columns of the state and walks the sequence's
-// tokens of this step in order, the state in registers: a warp holds 8 columns, its lanes are
-// 4 parts x 8 columns, part p holding rows p JPT .. p JPT + JPT of its column (d <= 4 JPT; rows
-// beyond d are zeros and stay zeros). The tokens' q, k and v come through shared memory in runs of
-// LA_RUN tokens, staged by the whole block; the 8 lanes of a quarter warp read the same q and k
-// words, so a 16-byte shared load serves them in one go. An output is the sum of its column's 4
-// parts, two shuffles. Every number depends on its own sequence only and is made in the same order
+// A block takes one sequence, one head and a few columns of the state and walks the sequence's
+// tokens of this step in order, the state in registers: a warp's lanes are PARTS parts x 32 / PARTS
+// columns, part p holding rows p JPT .. p JPT + JPT of its column (d <= PARTS JPT; rows beyond d
+// are zeros and stay zeros). The tokens' q, k and v come through shared memory in runs of LA_RUN
+// tokens, staged by the whole block; the lanes of a part read the same q and k words, so a 16-byte
+// shared load serves them in one go. An output is the sum of its column's parts, a few shuffles. Every number depends on its own sequence only and is made in the same order
 // whatever the step's division into tokens, so prompts fed whole, in portions or token by token
 // leave the same bits in the state.
+//
+// Two ways in. Steps of few tokens a sequence (decoding) read the projection's partial sums and apply
+// the activation while they stage a run. Prompts first go through linear_attn_prep_kernel, which adds
+// the partial sums and applies the activation ONCE for all blocks of a head (they share q and k) into
+// a dense float32 buffer; the walk then fetches run r + 1 with 16-byte asynchronous copies into a
+// second set of shared rows while it walks run r, and its token loop is unrolled so that a token's
+// shuffles overlap the next token's state update.
 #include "common.cuh"
 
-#define LA_COLS 32
 #define LA_RUN 16
 #define LA_THREADS 128
 
@@ -27,21 +32,44 @@ __device__ __forceinline__ float la_parts_sum(const float* p, int S, size_t stri
 }
 __device__ __forceinline__ float la_act(float x, int act) { return act ? x / (1.0f + expf(-x)) : x; }
 
-template <int JPT>
+// dense[n, c] = act(sum of the partial sums of u[n, c0 + c]) for the Wd columns of q, k and v.
+__global__ void __launch_bounds__(256)
+linear_attn_prep_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int q_col, int k_col, int v_col,
+                        int Hd, int Hdv, int act, float* __restrict__ dense, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const int Wd = 2 * Hd + Hdv;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long n = i / Wd;
+        const int c = (int)(i - n * Wd);
+        const int src = c < Hd ? q_col + c : (c < 2 * Hd ? k_col + c - Hd : v_col + c - 2 * Hd);
+        dense[i] = la_act(la_parts_sum(u + n * W + src, S, split_stride), act);
+    }
+}
+
+__device__ __forceinline__ void la_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// PRE: u is the dense buffer of linear_attn_prep_kernel (S = 1, no activation left to apply, q, k and v
+// at columns that are multiples of 4, d and dv multiples of 4). PARTS lanes share a column (d <= PARTS *
+// JPT), a warp holds CW = 32 / PARTS columns, a block 4 CW. In shared memory a token's q (and k) row is
+// PARTS segments of JPT + 4 values: the 4 values of padding put the segments that a warp reads together
+// on different banks (segments of 4 values need none: 32 lanes then read 512 bytes in a row).
+template <int JPT, int PARTS, bool PRE>
 __global__ void __launch_bounds__(LA_THREADS)
 linear_attn_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int q_col, int k_col, int v_col,
                    int act, const float* __restrict__ decay, float* __restrict__ state, size_t slot_stride,
                    const int* __restrict__ cu_q, const int* __restrict__ seq_slot, float* __restrict__ out, int H, int d,
                    int dv) {
-    constexpr int DR = 4 * JPT;                     // padded rows of q and k a token
-    extern __shared__ __align__(16) float sm[];     // q [LA_RUN][DR], k [LA_RUN][DR], v [LA_RUN][LA_COLS]
-    float* qs = sm;
-    float* ks = sm + LA_RUN * DR;
-    float* vs = sm + 2 * LA_RUN * DR;
+    constexpr int CW = 32 / PARTS, COLS = 4 * CW;   // columns a warp and a block
+    constexpr int SEG = JPT + (JPT == 4 ? 0 : 4), DR = PARTS * SEG;  // a part's segment and a token's row of q (or k)
+    constexpr int BUF = LA_RUN * (2 * DR + COLS);
+    extern __shared__ __align__(16) float sm[];     // q [LA_RUN][DR], k [LA_RUN][DR], v [LA_RUN][COLS]; twice when PRE
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int part = lane >> 3, e_local = lane & 7;
-    const int e0 = blockIdx.x * LA_COLS, h = blockIdx.y, b = blockIdx.z;
-    const int e = e0 + warp * 8 + e_local;
+    const int part = lane / CW, e_local = lane % CW;
+    const int e0 = blockIdx.x * COLS, h = blockIdx.y, b = blockIdx.z;
+    const int e = e0 + warp * CW + e_local;
     const float a = decay[h];
     pdl_trigger();
     pdl_wait();
@@ -54,31 +82,14 @@ linear_attn_kernel(const float* __restrict__ u, int S, size_t split_stride, int 
         const int j = part * JPT + i;
         st[i] = (j < d && e < dv) ? Sg[(size_t)j * dv + e] : 0.0f;
     }
-    for (int r0 = t0; r0 < t1; r0 += LA_RUN) {
-        const int nt = min(LA_RUN, t1 - r0);
-        __syncthreads();            // the run before has been walked
-        for (int i = tid; i < nt * DR; i += LA_THREADS) {
-            const int t = i / DR, j = i - t * DR;
-            float qv = 0.0f, kv = 0.0f;
-            if (j < d) {
-                const float* row = u + (size_t)(r0 + t) * W + h * d + j;
-                qv = la_act(la_parts_sum(row + q_col, S, split_stride), act);
-                kv = la_act(la_parts_sum(row + k_col, S, split_stride), act);
-            }
-            qs[i] = qv;
-            ks[i] = kv;
-        }
-        for (int i = tid; i < nt * LA_COLS; i += LA_THREADS) {
-            const int t = i / LA_COLS, c = i - t * LA_COLS;
-            vs[i] = e0 + c < dv
-                ? la_act(la_parts_sum(u + (size_t)(r0 + t) * W + v_col + h * dv + e0 + c, S, split_stride), act) : 0.0f;
-        }
-        __syncthreads();
+    // one run of staged tokens, walked in order
+    auto walk = [&](const float* qs, const float* ks, const float* vs, int r0, int nt) {
+#pragma unroll(PRE ? 4 : 1)
         for (int t = 0; t < nt; ++t) {
-            const float v = vs[t * LA_COLS + warp * 8 + e_local];
-            const float4* q4 = reinterpret_cast<const float4*>(qs + t * DR + part * JPT);
-            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DR + part * JPT);
-            float o0 = 0.0f, o1 = 0.0f;
+            const float v = vs[t * COLS + warp * CW + e_local];
+            const float4* q4 = reinterpret_cast<const float4*>(qs + t * DR + part * SEG);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DR + part * SEG);
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
             for (int i = 0; i < JPT / 4; ++i) {
                 const float4 q = q4[i], k = k4[i];
@@ -88,13 +99,74 @@ linear_attn_kernel(const float* __restrict__ u, int S, size_t split_stride, int 
                 st[4 * i + 3] = fmaf(a, st[4 * i + 3], k.w * v);
                 o0 = fmaf(st[4 * i], q.x, o0);
                 o1 = fmaf(st[4 * i + 1], q.y, o1);
-                o0 = fmaf(st[4 * i + 2], q.z, o0);
-                o1 = fmaf(st[4 * i + 3], q.w, o1);
+                o2 = fmaf(st[4 * i + 2], q.z, o2);
+                o3 = fmaf(st[4 * i + 3], q.w, o3);
             }
-            float o = o0 + o1;
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 16);
+            float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+            for (int x = CW; x < 32; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (part == 0 && e < dv) out[(size_t)(r0 + t) * H * dv + h * dv + e] = o;
+        }
+    };
+    if (PRE) {
+        // rows beyond d, the padding and columns beyond dv are zeros in both sets and are never copied over
+        for (int i = tid; i < 2 * BUF; i += LA_THREADS) sm[i] = 0.0f;
+        __syncthreads();
+        const int qc = d >> 2, pieces = 2 * qc + COLS / 4;       // 16-byte pieces a token: q, k, v
+        auto fetch = [&](int r0, int nt, float* buf) {
+            for (int i = tid; i < nt * pieces; i += LA_THREADS) {
+                const int t = i / pieces, c = i - t * pieces;
+                const float* row = u + (size_t)(r0 + t) * W;
+                if (c < 2 * qc) {
+                    const int j = 4 * (c < qc ? c : c - qc);          // JPT is a multiple of 4: a piece lies in one segment
+                    la_cp16(buf + (c < qc ? 0 : LA_RUN * DR) + t * DR + (j / JPT) * SEG + j % JPT,
+                            row + (c < qc ? q_col : k_col) + h * d + j);
+                } else if (e0 + 4 * (c - 2 * qc) < dv) {
+                    la_cp16(buf + 2 * LA_RUN * DR + t * COLS + 4 * (c - 2 * qc), row + v_col + h * dv + e0 + 4 * (c - 2 * qc));
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        fetch(t0, min(LA_RUN, t1 - t0), sm);
+        int which = 0;
+        for (int r0 = t0; r0 < t1; r0 += LA_RUN, which ^= 1) {
+            const int nt = min(LA_RUN, t1 - r0);
+            float* buf = sm + which * BUF;
+            if (r0 + LA_RUN < t1) {
+                fetch(r0 + LA_RUN, min(LA_RUN, t1 - r0 - LA_RUN), sm + (which ^ 1) * BUF);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
+            walk(buf, buf + LA_RUN * DR, buf + 2 * LA_RUN * DR, r0, nt);
+            __syncthreads();            // before the run after the next is copied over this one
+        }
+    } else {
+        float* qs = sm;
+        float* ks = sm + LA_RUN * DR;
+        float* vs = sm + 2 * LA_RUN * DR;
+        for (int r0 = t0; r0 < t1; r0 += LA_RUN) {
+            const int nt = min(LA_RUN, t1 - r0);
+            __syncthreads();            // the run before has been walked
+            for (int i = tid; i < nt * PARTS * JPT; i += LA_THREADS) {
+                const int t = i / (PARTS * JPT), j = i - t * (PARTS * JPT);
+                float qv = 0.0f, kv = 0.0f;
+                if (j < d) {
+                    const float* row = u + (size_t)(r0 + t) * W + h * d + j;
+                    qv = la_act(la_parts_sum(row + q_col, S, split_stride), act);
+                    kv = la_act(la_parts_sum(row + k_col, S, split_stride), act);
+                }
+                qs[t * DR + (j / JPT) * SEG + j % JPT] = qv;
+                ks[t * DR + (j / JPT) * SEG + j % JPT] = kv;
+            }
+            for (int i = tid; i < nt * COLS; i += LA_THREADS) {
+                const int t = i / COLS, c = i - t * COLS;
+                vs[i] = e0 + c < dv
+                    ? la_act(la_parts_sum(u + (size_t)(r0 + t) * W + v_col + h * dv + e0 + c, S, split_stride), act) : 0.0f;
+            }
+            __syncthreads();
+            walk(qs, ks, vs, r0, nt);
         }
     }
 #pragma unroll
@@ -105,32 +177,69 @@ linear_attn_kernel(const float* __restrict__ u, int S, size_t split_stride, int 
 }
 
 // Largest key size the kernel takes.
-LUMEN_API int lumen_linear_attn_max_dim() { return 4 * 64; }
+LUMEN_API int lumen_linear_attn_max_dim() { return 4 * 128; }
+
+// 1 if a step of N tokens in n_seqs sequences takes the prompt path (it then needs a dense float32
+// buffer of N (2 H d + H dv) values): at least LA_PRE_TOKENS tokens a sequence on average, head sizes
+// that are multiples of 4.
+#define LA_PRE_TOKENS 32
+LUMEN_API int lumen_linear_attn_wants_dense(int N, int n_seqs, int d, int dv) {
+    return (n_seqs > 0 && (long long)N >= (long long)LA_PRE_TOKENS * n_seqs && !(d & 3) && !(dv & 3)) ? 1 : 0;
+}
 
 // u: [S, N, W] partial sums; decay float32 [H]; state float32, sequence b's at state + seq_slot[b] *
-// slot_stride as [H][d][dv], updated in place; cu_q int32 [B + 1]; out float32 [N, H dv].
+// slot_stride as [H][d][dv], updated in place; cu_q int32 [B + 1]; out float32 [N, H dv]; dense: float32
+// scratch of N (2 H d + H dv) values, 16-byte aligned, or null for the direct path.
 LUMEN_API int lumen_linear_attn(const float* u, int n_split, long long split_stride, int W, int q_col, int k_col,
                                 int v_col, int act, const float* decay, float* state, long long slot_stride,
                                 const int* cu_q, const int* seq_slot, int n_seqs, float* out, int H, int d, int dv,
-                                cudaStream_t stream) {
+                                float* dense, int N, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (n_split < 1 || H <= 0 || d <= 0 || dv <= 0 || q_col < 0 || k_col < 0 || v_col < 0 || q_col + H * d > W ||
         k_col + H * d > W || v_col + H * dv > W)
         return LUMEN_ERR_BAD_ARGUMENT;
     if (d > lumen_linear_attn_max_dim() || H > 65535 || n_seqs > 65535) return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid((dv + LA_COLS - 1) / LA_COLS, H, n_seqs);
-#define LA_GO(JPT_)                                                                                                  \
+    const bool pre = dense != nullptr;
+    if (pre) {
+        if ((d & 3) || (dv & 3) || ((uintptr_t)dense & 15) || N <= 0) return LUMEN_ERR_BAD_ARGUMENT;
+        const long long total = (long long)N * (2 * H * d + H * dv);
+        long long blocks = (total + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        lumen_launch(linear_attn_prep_kernel, dim3((int)blocks), dim3(256), 0, stream, u, n_split, (size_t)split_stride, W,
+                     q_col, k_col, v_col, H * d, H * dv, act, dense, total);
+        LUMEN_LAUNCH_CHECK();
+        u = dense;
+        W = 2 * H * d + H * dv;
+        q_col = 0, k_col = H * d, v_col = 2 * H * d, act = 0, n_split = 1, split_stride = 0;
+    }
+    // Steps of few tokens: 4 lanes a column, a sector of the state a part. Prompts: 8 lanes a column, so a
+    // token's chain of sums is half as long and twice as many warps walk. (A whole warp a column, 25
+    // instructions a token and three or four warps a scheduler, was no faster for one prompt of 2,048
+    // tokens, 821 against 858 us at 16 heads of 128 x 128, and half as fast for four: every warp then reads
+    // the whole q and k rows from shared memory for one column's worth of sums.)
+#define LA_GO(JPT_, PARTS_, PRE_)                                                                                    \
     do {                                                                                                             \
-        const size_t smem = (size_t)LA_RUN * (2 * 4 * JPT_ + LA_COLS) * sizeof(float);                               \
-        auto kern = linear_attn_kernel<JPT_>;                                                                        \
+        constexpr int cols = 4 * (32 / PARTS_);                                                                      \
+        const size_t smem = (size_t)(PRE_ ? 2 : 1) * LA_RUN * (2 * PARTS_ * (JPT_ + (JPT_ == 4 ? 0 : 4)) + cols) * sizeof(float); \
+        auto kern = linear_attn_kernel<JPT_, PARTS_, PRE_>;                                                          \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-        lumen_launch(kern, grid, dim3(LA_THREADS), smem, stream, u, n_split, (size_t)split_stride, W, q_col, k_col,  \
-                     v_col, act, decay, state, (size_t)slot_stride, cu_q, seq_slot, out, H, d, dv);                  \
+        lumen_launch(kern, dim3((dv + cols - 1) / cols, H, n_seqs), dim3(LA_THREADS), smem, stream, u, n_split,      \
+                     (size_t)split_stride, W, q_col, k_col, v_col, act, decay, state, (size_t)slot_stride, cu_q,     \
+                     seq_slot, out, H, d, dv);                                                                       \
     } while (0)
-    if (d <= 32) LA_GO(8);
-    else if (d <= 64) LA_GO(16);
-    else if (d <= 128) LA_GO(32);
-    else LA_GO(64);
+    if (pre) {
+        if (d <= 32) LA_GO(4, 8, true);
+        else if (d <= 64) LA_GO(8, 8, true);
+        else if (d <= 128) LA_GO(16, 8, true);
+        else if (d <= 256) LA_GO(32, 8, true);
+        else LA_GO(64, 8, true);
+    } else {
+        if (d <= 32) LA_GO(8, 4, false);
+        else if (d <= 64) LA_GO(16, 4, false);
+        else if (d <= 128) LA_GO(32, 4, false);
+        else if (d <= 256) LA_GO(64, 4, false);
+        else LA_GO(128, 4, false);
+    }
 #undef LA_GO
     LUMEN_LAUNCH_CHECK();
     return 0;

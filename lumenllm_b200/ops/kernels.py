@@ -949,17 +949,25 @@ def clamped_glu(u, width, limit, alpha, out_dtype, token_gate_col=-1):
     return out
 
 
-def cols_rmsnorm(u, col, width, weight, eps, out_dtype):
+def cols_rmsnorm(u, col, width, weight, eps, out_dtype, gate=None, gate_col=0):
     """Columns col .. col + width of u (float32 [N, W] or partial sums, added) divided by their root
-    mean square (sqrt(mean(x^2) + eps)) times weight [width], in out_dtype."""
+    mean square (sqrt(mean(x^2) + eps)) times weight [width], in out_dtype; with `gate` (float32 [N, Wg]
+    or partial sums) also times sigmoid(gate[n, gate_col + c]), element by element."""
     u, S = _partials(u, "cols_rmsnorm.u")
     _, N, W = u.shape
+    hg = (0, 0, 0, 0, 0)
+    if gate is not None:
+        gate, gS = _partials(gate, "cols_rmsnorm.gate")
+        if gate.shape[1] != N or gate_col < 0 or gate_col + width > gate.shape[2]:
+            raise KernelError(f"cols_rmsnorm: gate {tuple(gate.shape)} has no {width} columns from {gate_col} for {N} rows")
+        hg = (ptr(gate), gS, N * gate.shape[2], gate.shape[2], int(gate_col))
     require(weight, F32, "cols_rmsnorm.weight")
     if weight.numel() != width or col < 0 or col + width > W:
         raise KernelError(f"cols_rmsnorm: {width} columns from {col} of rows of {W}, a weight of {weight.numel()}")
     out = torch.empty((N, int(width)), dtype=out_dtype, device=u.device)
-    f = fn("head_ops", "lumen_cols_rmsnorm", [P, c_int, c_longlong, c_int, c_int, c_int, P, c_float, P, c_int, c_int, P])
-    check(f(ptr(u), S, N * W, W, int(col), int(width), ptr(weight), float(eps), ptr(out), _is_bf16(out), N,
+    f = fn("head_ops", "lumen_cols_rmsnorm", [P, c_int, c_longlong, c_int, c_int, c_int, P, c_float, P, c_int, c_int,
+                                              P, c_int, c_longlong, c_int, c_int, P])
+    check(f(ptr(u), S, N * W, W, int(col), int(width), ptr(weight), float(eps), ptr(out), _is_bf16(out), N, *hg,
             stream_ptr()), "cols_rmsnorm")
     return out
 
@@ -1036,12 +1044,16 @@ def linear_attn(u, q_col, k_col, v_col, silu, decay, state, cu_q, seq_slot, n_se
     if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs:
         raise KernelError("linear_attn: metadata does not match the batch")
     out = torch.empty((N, heads * dv), dtype=F32, device=u.device)
+    # prompts: the activated q, k and v once for all blocks, in a dense buffer that the walk copies from
+    dense = None
+    if int_fn("linear_attn", "lumen_linear_attn_wants_dense", [c_int, c_int, c_int, c_int])(N, int(n_seqs), int(d), int(dv)):
+        dense = torch.empty((N, 2 * heads * d + heads * dv), dtype=F32, device=u.device)
     f = fn("linear_attn", "lumen_linear_attn",
            [P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P, P, c_longlong, P, P, c_int, P, c_int, c_int,
-            c_int, P])
+            c_int, P, c_int, P])
     check(f(ptr(u), S, N * W, W, int(q_col), int(k_col), int(v_col), 1 if silu else 0, ptr(decay), ptr(state),
-            state.stride(0), ptr(cu_q), ptr(seq_slot), int(n_seqs), ptr(out), int(heads), int(d), int(dv), stream_ptr()),
-          "linear_attn")
+            state.stride(0), ptr(cu_q), ptr(seq_slot), int(n_seqs), ptr(out), int(heads), int(d), int(dv), ptr(dense), N,
+            stream_ptr()), "linear_attn")
     return out
 
 

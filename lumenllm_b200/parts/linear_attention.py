@@ -78,8 +78,6 @@ class DecayLinearAttention:
         o = K.linear_attn(u, 0, self.k_col, self.v_col, self.silu, self.decay, S, ctx.cu_q, ctx.seq_slot, ctx.B,
                           self.H, self.d, self.dv)
         dt = self.runtime.dtype
-        if self.gated:
-            v = K.head_norm_gate(o, self.norm_w, self.eps, u, self.g_col, 1, dt)      # one "head": the whole row
-        else:
-            v = K.cols_rmsnorm(o, 0, self.H * self.dv, self.norm_w, self.eps, dt)
+        v = K.cols_rmsnorm(o, 0, self.H * self.dv, self.norm_w, self.eps, dt, gate=u if self.gated else None,
+                           gate_col=self.g_col)
         return self.o(v, split_ok=True, add_to=residual)
