@@ -316,6 +316,7 @@ class VekolixConfig:
                 else:
                     params = {"hidden_size": D, "expert_size": f.ff, "num_experts": f.experts, "top": f.top,
                               "scale": 1.0, "router": "sigmoid", "correction": False, "weight_on": "input",
+                              "update_in_pieces": True,
                               "expert": {"kind": "clamped_glu", "limit": f.limit, "alpha": GLU_ALPHA}}
                     if f.shared_ff:
                         params["shared"] = {"size": f.shared_ff, "kind": "clamped_glu", "limit": f.shared_limit,

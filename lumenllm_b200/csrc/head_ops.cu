@@ -709,20 +709,20 @@ LUMEN_API int lumen_clamped_glu(const float* u, int n_split, long long split_str
 // columns of a projection (partial sums [S, N, W]), in the run's type; with a gate (partial sums [gS, N,
 // gW]) also times sigmoid(gate[n, g0 + c]). A block a token.
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 cols_rmsnorm_kernel(const float* __restrict__ u, int S, size_t split_stride, int W, int c0, int C,
                     const float* __restrict__ w, float eps, TO* __restrict__ out, const float* __restrict__ gate, int gS,
                     size_t g_split_stride, int gW, int g0) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
-    const int n = blockIdx.x;
+    const int n = blockIdx.x, nt = blockDim.x;
     const float* src = u + (size_t)n * W + c0;
-    // a thread's values stay in registers where a row is at most 4 x 256 wide
+    // a thread's values stay in registers where a row is at most 4 x the block wide
     float keep[4];
     float ss = 0.0f;
     int k = 0;
-    for (int c = threadIdx.x; c < C; c += 256, ++k) {
+    for (int c = threadIdx.x; c < C; c += nt, ++k) {
         const float x = parts_sum(src + c, S, split_stride);
         if (k < 4) keep[k] = x;
         ss += x * x;
@@ -730,7 +730,7 @@ cols_rmsnorm_kernel(const float* __restrict__ u, int S, size_t split_stride, int
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)C + eps);
     k = 0;
-    for (int c = threadIdx.x; c < C; c += 256, ++k) {
+    for (int c = threadIdx.x; c < C; c += nt, ++k) {
         const float x = k < 4 ? keep[k] : parts_sum(src + c, S, split_stride);
         float y = x * inv * w[c];
         if (gate) y *= sigmoid_f(parts_sum(gate + (size_t)n * gW + g0 + c, gS, g_split_stride));
@@ -745,11 +745,19 @@ LUMEN_API int lumen_cols_rmsnorm(const float* u, int n_split, long long split_st
     if (N <= 0) return 0;
     if (n_split < 1 || C <= 0 || c0 < 0 || c0 + C > W) return LUMEN_ERR_BAD_ARGUMENT;
     if (gate && (gate_split < 1 || gate_col < 0 || gate_col + C > gate_w)) return LUMEN_ERR_BAD_ARGUMENT;
+    // few rows (decode steps): a row cannot fill the device, so its block is made wide and a thread's chain
+    // of loads (a value's partial sums, one after the other) short
+    int threads = 256;
+    if (N < 2 * 148) {
+        threads = ((C + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        if (threads < 128) threads = 128;
+    }
     if (out_is_bf16)
-        lumen_launch(cols_rmsnorm_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride,
+        lumen_launch(cols_rmsnorm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, u, n_split, (size_t)split_stride,
                      W, c0, C, w, eps, (__nv_bfloat16*)out, gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col);
     else
-        lumen_launch(cols_rmsnorm_kernel<float>, dim3(N), dim3(256), 0, stream, u, n_split, (size_t)split_stride, W, c0,
+        lumen_launch(cols_rmsnorm_kernel<float>, dim3(N), dim3(threads), 0, stream, u, n_split, (size_t)split_stride, W, c0,
                      C, w, eps, (float*)out, gate, gate_split, (size_t)gate_split_stride, gate_w, gate_col);
     LUMEN_LAUNCH_CHECK();
     return 0;

@@ -38,7 +38,9 @@ router output by itself, s = sigmoid(logit), instead of the softmax; `correction
 sum expert(w y), which the gated product does by multiplying its two sums by w before the
 activation; `expert` {"kind": "clamped_glu", "limit", "alpha"}: the experts are clamped gated
 units as above instead of SwiGLU; `shared` {"size", "kind", "limit", "alpha", "token_gate"}: the
-shared expert's own form.
+shared expert's own form; `update_in_pieces`: the routed experts' and the shared expert's updates are
+handed on as a list of two stacks instead of being copied into one (for arrangements that add a
+list's pieces, parts/block.py "pre_norm").
 """
 from __future__ import annotations
 
@@ -297,6 +299,7 @@ class RoutedExperts:
         self.w_gate_up = torch.cat([gate, up], dim=1).contiguous()          # [E, 2 F, D]: gate rows, then up rows
         self.w_down = stack([f"{pre}.e{e}.down" for e in range(self.E)])    # [E, D, F]
         self.shared = build_part("ffn", self._shared_spec(spec), weights, runtime) if Fs else None
+        self.update_in_pieces = bool(p.get("update_in_pieces", False))
 
     adds_residual = True      # forward takes `residual`; the shared expert may add its update there in place
 
@@ -318,4 +321,6 @@ class RoutedExperts:
         s = self.shared.forward(y, ctx, residual=residual)
         if s is None:
             return out
+        if self.update_in_pieces:
+            return [out, s]       # the arrangement adds the pieces as they are (no copy into one stack)
         return torch.cat([out, s if s.dim() == 3 else s.unsqueeze(0)], dim=0)

@@ -58,6 +58,8 @@ def total(update):
     from lumenllm_b200.parts.norm import ScaledUpdate
     if isinstance(update, ScaledUpdate):
         return sum(s * total(d) for d, s in update.groups)
+    if isinstance(update, (list, tuple)):
+        return sum(total(d) for d in update)
     return (update.sum(0) if update.dim() == 3 else update).float().cpu()
 
 
