@@ -134,13 +134,18 @@ latent_store_kernel(const float* __restrict__ u, int S, size_t split_stride, int
     const int page = block_table[(size_t)tok_seq[n] * bt_stride + cp / LUMEN_PAGE];
     T* row = cache + ((size_t)page * LUMEN_PAGE + cp % LUMEN_PAGE) * (R + r);
     float ss = 0.0f;
-    for (int e = tid; e < R; e += 128) {
+    float keep[4];              // a latent of up to 512 stays in registers between the two passes
+    int k = 0;
+    for (int e = tid; e < R; e += 128, ++k) {
         const float x = parts_sum(src + e, S, split_stride);
+        if (k < 4) keep[k] = x;
         ss += x * x;
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)R + eps);
-    for (int e = tid; e < R; e += 128) row[e] = from_f32<T>(parts_sum(src + e, S, split_stride) * inv * nw[e]);
+    k = 0;
+    for (int e = tid; e < R; e += 128, ++k)
+        row[e] = from_f32<T>((k < 4 ? keep[k] : parts_sum(src + e, S, split_stride)) * inv * nw[e]);
     const int half = rot >> 1;
     const float2* csn = cs + (size_t)n * half;
     for (int i = tid; i < half; i += 128) {

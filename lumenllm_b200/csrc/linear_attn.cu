@@ -23,6 +23,7 @@
 #include "common.cuh"
 
 #define LA_RUN 16
+#define LA_GROUP 8
 #define LA_THREADS 128
 
 __device__ __forceinline__ float la_parts_sum(const float* p, int S, size_t stride) {
@@ -85,30 +86,57 @@ linear_attn_kernel(const float* __restrict__ u, int S, size_t split_stride, int 
         const int j = part * JPT + i;
         st[i] = (j < d && e < dv) ? Sg[(size_t)j * dv + e] : 0.0f;
     }
-    // one run of staged tokens, walked in order
-    auto walk = [&](const float* qs, const float* ks, const float* vs, int r0, int nt) {
-#pragma unroll(PRE ? 4 : 1)
-        for (int t = 0; t < nt; ++t) {
-            const float v = vs[t * COLS + warp * CW + e_local];
-            const float4* q4 = reinterpret_cast<const float4*>(qs + t * DR + part * SEG);
-            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DR + part * SEG);
-            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+    // one token: the state moves on; what comes back is this part's share of the column's output
+    auto token = [&](const float* qs, const float* ks, const float* vs, int t) -> float {
+        const float v = vs[t * COLS];
+        const float4* q4 = reinterpret_cast<const float4*>(qs + t * DR);
+        const float4* k4 = reinterpret_cast<const float4*>(ks + t * DR);
+        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < JPT / 4; ++i) {
-                const float4 q = q4[i], k = k4[i];
-                st[4 * i] = fmaf(a, st[4 * i], k.x * v);
-                st[4 * i + 1] = fmaf(a, st[4 * i + 1], k.y * v);
-                st[4 * i + 2] = fmaf(a, st[4 * i + 2], k.z * v);
-                st[4 * i + 3] = fmaf(a, st[4 * i + 3], k.w * v);
-                o0 = fmaf(st[4 * i], q.x, o0);
-                o1 = fmaf(st[4 * i + 1], q.y, o1);
-                o2 = fmaf(st[4 * i + 2], q.z, o2);
-                o3 = fmaf(st[4 * i + 3], q.w, o3);
+        for (int i = 0; i < JPT / 4; ++i) {
+            const float4 q = q4[i], k = k4[i];
+            st[4 * i] = fmaf(a, st[4 * i], k.x * v);
+            st[4 * i + 1] = fmaf(a, st[4 * i + 1], k.y * v);
+            st[4 * i + 2] = fmaf(a, st[4 * i + 2], k.z * v);
+            st[4 * i + 3] = fmaf(a, st[4 * i + 3], k.w * v);
+            o0 = fmaf(st[4 * i], q.x, o0);
+            o1 = fmaf(st[4 * i + 1], q.y, o1);
+            o2 = fmaf(st[4 * i + 2], q.z, o2);
+            o3 = fmaf(st[4 * i + 3], q.w, o3);
+        }
+        return (o0 + o1) + (o2 + o3);
+    };
+    // One run of staged tokens, walked in order. A warp issues in order, so a token's chain of shuffles
+    // (each waits for the one before) would hold up the next token's sums: LA_GROUP tokens' shares are
+    // kept and summed over the parts together, their chains side by side. A full run is unrolled.
+    auto walk = [&](const float* qs, const float* ks, const float* vs, int r0, int nt) {
+        qs += part * SEG;
+        ks += part * SEG;
+        vs += warp * CW + e_local;
+        float* orow = out + (size_t)r0 * H * dv + h * dv + e;
+        const bool writes = part == 0 && e < dv;
+        int t = 0;
+        if (nt == LA_RUN) {
+#pragma unroll
+            for (int g0 = 0; g0 < LA_RUN; g0 += LA_GROUP) {
+                float o[LA_GROUP];
+#pragma unroll
+                for (int g = 0; g < LA_GROUP; ++g) o[g] = token(qs, ks, vs, g0 + g);
+#pragma unroll
+                for (int x = CW; x < 32; x <<= 1)
+#pragma unroll
+                    for (int g = 0; g < LA_GROUP; ++g) o[g] += __shfl_xor_sync(0xffffffffu, o[g], x);
+                if (writes)
+#pragma unroll
+                    for (int g = 0; g < LA_GROUP; ++g) orow[(size_t)(g0 + g) * H * dv] = o[g];
             }
-            float o = (o0 + o1) + (o2 + o3);
+            t = LA_RUN;
+        }
+        for (; t < nt; ++t) {
+            float o = token(qs, ks, vs, t);
 #pragma unroll
             for (int x = CW; x < 32; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-            if (part == 0 && e < dv) out[(size_t)(r0 + t) * H * dv + h * dv + e] = o;
+            if (writes) orow[(size_t)t * H * dv] = o;
         }
     };
     if (PRE) {
@@ -216,10 +244,10 @@ LUMEN_API int lumen_linear_attn(const float* u, int n_split, long long split_str
         q_col = 0, k_col = H * d, v_col = 2 * H * d, act = 0, n_split = 1, split_stride = 0;
     }
     // Steps of few tokens: 4 lanes a column, a sector of the state a part. Prompts: 8 lanes a column, so a
-    // token's chain of sums is half as long and twice as many warps walk. (A whole warp a column, 25
-    // instructions a token and three or four warps a scheduler, was no faster for one prompt of 2,048
-    // tokens, 821 against 858 us at 16 heads of 128 x 128, and half as fast for four: every warp then reads
-    // the whole q and k rows from shared memory for one column's worth of sums.)
+    // token's chain of sums is half as long and twice as many warps walk. (16 lanes a column, two warps a
+    // scheduler: 424 us as with 8 for one prompt of 2,048 tokens at 16 heads of 128 x 128, but 613 against
+    // 546 us at 32 heads and 1,108 against 834 us for four prompts: every warp reads the whole q and k rows
+    // from shared memory, for half as many columns' worth of sums.)
 #define LA_GO(JPT_, PARTS_, PRE_)                                                                                    \
     do {                                                                                                             \
         constexpr int cols = 4 * (32 / PARTS_);                                                                      \

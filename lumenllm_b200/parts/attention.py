@@ -283,7 +283,10 @@ class HeadNormAttention:
         self.gated = bool(p.get("output_gate", False))
         if self.gated:
             mats.append(weights[f"{pre}.g"])       # the gate reads the same rows: one product for all four
-        self.proj = Linear.stacked(mats, runtime)
+        # `external_projection`: whoever runs this part makes the product (stacked with others that read
+        # the same rows) and hands its result to forward; these are the matrices, in the order of the columns
+        self.input_mats = mats if p.get("external_projection", False) else None
+        self.proj = None if self.input_mats is not None else Linear.stacked(mats, runtime)
         self.bias = (torch.cat([f32(f"{pre}.q.b"), f32(f"{pre}.k.b"), f32(f"{pre}.v.b")]).contiguous()
                      if p.get("bias", False) else None)
         self.q_norm = self.k_norm = None
@@ -300,9 +303,15 @@ class HeadNormAttention:
 
     adds_residual = True      # forward takes `residual` and may add its update to it in place
 
-    def forward(self, y, ctx, entry, residual=None):
+    projects_input = True         # may be built with `external_projection` and fed `projected`
+    needs_first_columns = True    # its kernels read q, k, v (and the gate) from column 0 of the projection's rows
+
+    def forward(self, y, ctx, entry, residual=None, projected=None, col0=0):
         kc, vc, table = entry.cache()
-        u = self.proj(y, split_ok=True)            # float32 [q | k | v | gate], possibly partial sums
+        if projected is not None and col0 != 0:
+            raise ValueError("head_norm_attention reads its columns from the start of the projection's rows")
+        # float32 [q | k | v | gate | ...], possibly partial sums
+        u = projected if projected is not None else self.proj(y, split_ok=True)
         rot = self.position.rotary_dim
         q = K.qkv_head_norm_store(u, self.bias, self.q_norm, self.k_norm, self.eps,
                                   self.position.angles(ctx) if rot else None, rot, ctx.cache_pos, ctx.tok_seq, table,

@@ -57,7 +57,11 @@ class DecayLinearAttention:
         pre = spec.prefix
         f32 = lambda n: weights[n].to(device=runtime.device, dtype=torch.float32).contiguous()
         self.decay = torch.tensor(decay, dtype=torch.float32, device=runtime.device)
-        self.proj = Linear.stacked([weights[f"{pre}.{n}"] for n in ("q", "k", "v") + (("g",) if self.gated else ())], runtime)
+        mats = [weights[f"{pre}.{n}"] for n in ("q", "k", "v") + (("g",) if self.gated else ())]
+        # `external_projection`: whoever runs this part makes the product (stacked with others that read
+        # the same rows) and hands its result, and the column where this part's begin, to forward
+        self.input_mats = mats if p.get("external_projection", False) else None
+        self.proj = None if self.input_mats is not None else Linear.stacked(mats, runtime)
         self.norm_w = f32(f"{pre}.norm")
         self.o = Linear(weights[f"{pre}.o"], runtime)
         self.k_col, self.v_col = self.H * self.d, 2 * self.H * self.d
@@ -72,12 +76,15 @@ class DecayLinearAttention:
 
     adds_residual = True      # forward takes `residual` and may add its update to it in place
 
-    def forward(self, y, ctx, entry, residual=None):
+    projects_input = True         # may be built with `external_projection` and fed `projected`
+
+    def forward(self, y, ctx, entry, residual=None, projected=None, col0=0):
         S = entry.state()
-        u = self.proj(y, split_ok=True)                     # float32 [q | k | v | g], possibly partial sums
-        o = K.linear_attn(u, 0, self.k_col, self.v_col, self.silu, self.decay, S, ctx.cu_q, ctx.seq_slot, ctx.B,
-                          self.H, self.d, self.dv)
+        # float32 [... | q | k | v | g | ...] from column col0, possibly partial sums
+        u = projected if projected is not None else self.proj(y, split_ok=True)
+        o = K.linear_attn(u, col0, col0 + self.k_col, col0 + self.v_col, self.silu, self.decay, S, ctx.cu_q, ctx.seq_slot,
+                          ctx.B, self.H, self.d, self.dv)
         dt = self.runtime.dtype
         v = K.cols_rmsnorm(o, 0, self.H * self.dv, self.norm_w, self.eps, dt, gate=u if self.gated else None,
-                           gate_col=self.g_col)
+                           gate_col=col0 + self.g_col)
         return self.o(v, split_ok=True, add_to=residual)

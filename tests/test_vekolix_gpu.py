@@ -281,6 +281,9 @@ def test_two_mixers_side_by_side(dtype):
     m = parallel(SOFTMAX[0], LINEAR[3], 0.8, -1.3)
     part, w = mixer_part(m, D, dtype, seed=15)
     assert part.cache_need().n_kv == 2 and part.state_shape()[0] == (5, 8, 40)
+    # both sides start with a product of the same rows: ONE product, the linear side's columns behind the other's
+    assert part.proj is not None and part.col0 == [0, 4 * 16 + 2 * (16 + 24)] and part.mixers[0].proj is None
+    assert part.proj.out_features == part.col0[1] + 2 * 5 * 8 + 2 * 5 * 40
     in_any_portions(part, runtime(dtype), lambda y: P.side_by_side(y, w, "l0.mix", m, 1e-6, torch.arange(y.shape[0])),
                     D, dtype, seed=16)
 
