@@ -119,8 +119,8 @@ def lebelix_config(s):
 
 def vekolix_config(s):
     left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
-            "rot": {"base": 500000.0, "dims": s["rot"],
-                    "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 1000000.0, "dims": s["rot"],
+                    "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}}
     n = s["linear"]["heads"]
     right = dict(s["linear"], decay=[1.0 - 2.0 ** (-2.0 - 8.0 * h / max(n - 1, 1)) for h in range(n)])
     side = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.9}
@@ -133,7 +133,7 @@ def vekolix_config(s):
     layers = [{"type": "parallel" if p[0] == "p" else "latent_attention", "mixer": side if p[0] == "p" else lat,
                "mlp": {"kind": "dense", "ff": s["ff"]} if p[1] == "d" else experts} for p in s["pattern"]]
     return {"architecture": "Vekolix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.8, "logit_scale": 0.5, "logit_softcap": 30.0, "max_positions": CONTEXT, "layers": layers}
+            "residual_mult": 0.8, "logit_scale": 0.5, "logit_softcap": 40.0, "max_positions": CONTEXT, "layers": layers}
 
 
 def qwen3_config(s):

@@ -583,10 +583,10 @@ def test_a_long_wide_prompt(tmp_path):
     from lumenllm_b200.engine import Engine, StepEntry
     for mult in (1.0, 0.5):
         cfg = config(64, 1024, 1e-6, [
-            layer(parallel(softmax_side(4, 2, 128, 128, 0.09, rot=64, scaling=(8.0, 1024, 32.0, 1.0)),
-                           linear_side(4, 64, 64, (0.9, 0.99, 0.999, 0.5)), 0.6, 1.1), dense(512)),
+            layer(parallel(softmax_side(4, 2, 128, 128, 0.09, rot=64, scaling=(6.0, 512, 24.0, 1.5)),
+                           linear_side(4, 64, 64, (0.9, 0.99, 0.995, 0.5)), 0.65, 1.15), dense(512)),
             layer(latent(4, 64, 32, 64, 256, 192, 0.1, rot=32), moe(8, 2, 128, 1.0, shared=(128, 2.0)))],
-            mult=mult, logit_scale=0.25, softcap=30.0)
+            mult=mult, logit_scale=0.35, softcap=20.0)
         cfg = calm(cfg)
         T = 2300
         folder = write_model(cfg, tmp_path / f"wide{mult}", seed=70)
